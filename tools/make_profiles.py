@@ -1,4 +1,4 @@
-"""Summarise an .ncu-rep (raw page) and the SASS of libdsb200.so into profiles/ (tracked evidence)."""
+"""Summarise an .ncu-rep (raw page) into profiles/ (tracked evidence)."""
 import csv
 import io
 import os
@@ -41,49 +41,7 @@ def ncu_summary(rep, out_md, title):
     open(out_md, "w").write("\n".join(lines) + "\n")
 
 
-def sass_summary(out_md):
-    so = os.path.join(ROOT, "deepspeedsyclsupport_b200", "lib", "libdsb200.so")
-    sass = subprocess.run(["cuobjdump", "-sass", so], capture_output=True, text=True).stdout
-    cur = None
-    per = {}
-    for line in sass.splitlines():
-        m = re.search(r"Function : (\S+)", line)
-        if m:
-            cur = m.group(1)
-            per[cur] = Counter()
-            continue
-        if cur is None:
-            continue
-        m = re.search(r"^\s+/\*[0-9a-f]+\*/\s+(?:@!?U?P\d+\s+)?([A-Z0-9_.]+)", line)
-        if m:
-            op = m.group(1)
-            for key in ("UTCHMMA", "UTCQMMA", "UTCCP", "UTCBAR", "UTMALDG", "UTMASTG", "UTMAREDG", "UBLKCP", "LDTM", "STTM", "UTCATOMSWS", "HMMA", "SYNCS",
-                        "LDG", "STG", "LDGSTS", "MUFU", "ATOM", "RED"):
-                if op.startswith(key):
-                    per[cur][key] += 1
-            if "MC" in op.split(".")[0] or ".MC" in op or "LDGMC" in op:
-                per[cur]["MULTIMEM"] += 1
-            if op.startswith("UTCHMMA") and ".2CTA" in op:
-                per[cur]["2CTA"] += 1
-    lines = ["# SASS evidence (cuobjdump -sass libdsb200.so, sm_100a)", "",
-             "Counts of Blackwell-specific mnemonics per kernel: `UTCHMMA` = tcgen05.mma (bf16; `.2CTA` = cta_group::2 pair MMA), `UTMALDG/UTMASTG/UTMAREDG` = TMA "
-             "load/store/reduce, `LDTM/STTM` = tcgen05.ld/st, `SYNCS` = mbarrier ops, `HMMA` = legacy mma.sync (must be 0).", "",
-             "`UTCQMMA` = tcgen05.mma block-scaled (mxf8f6f4.block_scale), `UTCCP` = tcgen05.cp (smem -> TMEM), `UBLKCP` = cp.async.bulk, "
-             "`MULTIMEM` = multimem.ld_reduce / multimem.st (NVLS: LDGMC / STG...MC forms).", "",
-             "| kernel | UTCHMMA | of which .2CTA | UTCQMMA | UTCCP | UTMALDG | UTMASTG | UTMAREDG | UBLKCP | LDTM | STTM | SYNCS | MULTIMEM | HMMA | LDG | STG |",
-             "|---|---|---|---|---|---|---|---|---|---|---|---|---|---|---|---|"]
-    for k, c in sorted(per.items()):
-        if sum(c.values()) == 0:
-            continue
-        dem = subprocess.run(["c++filt", k], capture_output=True, text=True).stdout.strip()
-        dem = re.sub(r"\(.*", "", dem)[:90]
-        lines.append(f"| `{dem}` | {c['UTCHMMA']} | {c['2CTA']} | {c['UTCQMMA']} | {c['UTCCP']} | {c['UTMALDG']} | {c['UTMASTG']} | {c['UTMAREDG']} | {c['UBLKCP']} | "
-                     f"{c['LDTM']} | {c['STTM']} | {c['SYNCS']} | {c['MULTIMEM']} | {c['HMMA']} | {c['LDG']} | {c['STG']} |")
-    open(out_md, "w").write("\n".join(lines) + "\n")
-
-
 if __name__ == "__main__":
     os.makedirs(os.path.join(ROOT, "profiles"), exist_ok=True)
     if len(sys.argv) > 1:
         ncu_summary(sys.argv[1], os.path.join(ROOT, "profiles", sys.argv[2]), sys.argv[3] if len(sys.argv) > 3 else "ncu summary")
-    sass_summary(os.path.join(ROOT, "profiles", "sass_evidence.md"))
