@@ -21,7 +21,7 @@ def ncu_summary(rep, out_md, title):
     raw = subprocess.run(["ncu", "-i", rep, "--page", "raw", "--csv"], capture_output=True, text=True).stdout
     rows = list(csv.reader(io.StringIO(raw)))
     hdr, units = rows[0], rows[1]
-    lines = [f"# {title}", "", f"source: `{os.path.basename(rep)}` (ncu --set full --clock-control none --import-source on), B200", ""]
+    lines = [f"# {title}", "", f"source: `{os.path.basename(rep)}` (ncu --set full --clock-control none), B200", ""]
     seen = Counter()
     for r in rows[2:]:
         name = r[hdr.index("Kernel Name")]
