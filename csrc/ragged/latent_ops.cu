@@ -1,0 +1,698 @@
+// build: precise-math
+// Ragged-batch kernels for decoders that keep an fp32 residual stream, cache one low-rank latent per token instead of
+// per-head keys and values, and route tokens with a grouped, bias-corrected top-k router.  Every kernel takes its sizes
+// as arguments (no size is assumed to be a power of two or a multiple of a vector width) and exists for 16-bit (bf16)
+// and 32-bit activations; sums, norms, softmax and router scores are always fp32.
+//
+//   embed_sinusoid        token table lookup + sinusoidal position vector -> fp32 residual
+//   sandwich_norm         x += rms(y) * (wb + ob)   and / or   out = rms(x) * (w + o)      (one pass per token row)
+//   latent_norm_append    plain-weight RMS norm of the query latent and of the key/value latent of every token; the
+//                         key/value latent goes straight into its slot of the paged latent cache
+//   latent_attention      softmax(q_abs . c) c over the paged latent cache: all heads of a token share the cached rows
+//                         (keys and values are the same row), causal, split along the keys + merge
+//   sigmoid_gate_mul      a *= sigmoid(g)
+//   grouped_topk_gating   softmax scores (+ correction for the choice only), best `keep` of `groups` neighbour groups by
+//                         their largest choice score, top-k of the surviving experts, weights = uncorrected scores
+//   moe_scatter / moe_gather   expert-sorted copies and the weighted fp32 combine, any width
+//   clamped_swish_gate    min(g, L) * sigmoid(alpha * min(g, L)) * (clamp(u, -L, L) + shift)
+//   moe_gemm_rows         grouped expert GEMM on CUDA cores (fp32 accumulation) for shapes / dtypes the tensor-core
+//                         grouped GEMM does not take
+//   softcap               logits = cap * tanh(logits / cap)
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "../common/host.h"
+
+namespace dsb {
+namespace latent {
+
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// sum over the block; every thread gets the result.  `red` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // red may still be read from an earlier call
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+// ---------------------------------------------------------------------------------------------------------------- embedding
+template <typename TW>
+__global__ void embed_sinusoid_kernel(const long long* __restrict__ ids, const TW* __restrict__ table, const int* __restrict__ tok_pos,
+                                      const double* __restrict__ freq, float* __restrict__ out, int dim) {
+  const int t = blockIdx.x;
+  const long long id = ids[t];
+  const double p = static_cast<double>(tok_pos[t]);
+  const TW* row = table + id * dim;
+  float* o = out + static_cast<size_t>(t) * dim;
+  for (int i = threadIdx.x; 2 * i < dim; i += blockDim.x) {
+    double s, c;
+    sincos(p * freq[i], &s, &c);
+    o[2 * i] = to_f(row[2 * i]) + static_cast<float>(s);
+    if (2 * i + 1 < dim) o[2 * i + 1] = to_f(row[2 * i + 1]) + static_cast<float>(c);
+  }
+}
+
+// --------------------------------------------------------------------------------------------------------------------- norms
+// Row r of the fp32 residual (row rows[r] when `rows` is given; then nothing is written back to x):
+//   y given:   x <- x + y / sqrt(mean(y^2) + eps) * (wb + ob)
+//   w given:   out <- x / sqrt(mean(x^2) + eps) * (w + o)
+template <typename TY, typename TO>
+__global__ void sandwich_norm_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ wb, float ob,
+                                     const float* __restrict__ w, float o, TO* __restrict__ out, const int* __restrict__ rows, int dim,
+                                     float eps) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  float* xr = x + static_cast<size_t>(rows ? rows[r] : r) * dim;
+  float sx = 0.f;
+  if (y != nullptr) {
+    const TY* yr = y + static_cast<size_t>(r) * dim;
+    float sy = 0.f;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+      const float v = to_f(yr[c]);
+      sy += v * v;
+    }
+    sy = block_sum(sy, red);
+    const float inv = 1.f / sqrtf(sy / static_cast<float>(dim) + eps);
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+      const float v = xr[c] + to_f(yr[c]) * inv * (wb[c] + ob);
+      xr[c] = v;  // read back below by this same thread only
+      sx += v * v;
+    }
+  } else if (w != nullptr) {
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+      const float v = xr[c];
+      sx += v * v;
+    }
+  }
+  if (w == nullptr) return;
+  sx = block_sum(sx, red);
+  const float inv = 1.f / sqrtf(sx / static_cast<float>(dim) + eps);
+  TO* orow = out + static_cast<size_t>(r) * dim;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) orow[c] = from_f<TO>(xr[c] * inv * (w[c] + o));
+}
+
+// One warp per (token, which): which = 0 normalises lat[t, :nq] with wq into cq[t, :]; which = 1 normalises
+// lat[t, nq : nq + nkv] with wkv into the token's row of the paged cache [blocks, block_size, nkv].
+template <typename T>
+__global__ void latent_norm_append_kernel(const T* __restrict__ lat, int ld, const float* __restrict__ wq, const float* __restrict__ wkv,
+                                          T* __restrict__ cq, T* __restrict__ cache, const int* __restrict__ tok_seq,
+                                          const int* __restrict__ tok_pos, const int* __restrict__ block_table, int bt_stride,
+                                          int block_size, int n_tokens, int nq, int nkv, float eps) {
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int t = gw >> 1, which = gw & 1;
+  if (t >= n_tokens) return;
+  const int n = which ? nkv : nq;
+  if (n == 0) return;
+  const T* src = lat + static_cast<size_t>(t) * ld + (which ? nq : 0);
+  const float* w = which ? wkv : wq;
+  T* dst;
+  if (which) {
+    const int pos = tok_pos[t];
+    const int blk = block_table[static_cast<size_t>(tok_seq[t]) * bt_stride + pos / block_size];
+    dst = cache + (static_cast<size_t>(blk) * block_size + pos % block_size) * nkv;
+  } else {
+    dst = cq + static_cast<size_t>(t) * nq;
+  }
+  float s = 0.f;
+  for (int c = lane; c < n; c += 32) {
+    const float v = to_f(src[c]);
+    s += v * v;
+  }
+  s = warp_sum(s);
+  const float inv = 1.f / sqrtf(s / static_cast<float>(n) + eps);
+  for (int c = lane; c < n; c += 32) dst[c] = from_f<T>(to_f(src[c]) * inv * w[c]);
+}
+
+// ----------------------------------------------------------------------------------------------------------- latent attention
+// Grid (token, split, head group of 8).  4 warps; warp w owns heads hg*8 + w and hg*8 + w + 4.  Keys come in tiles of 32 rows of
+// the latent cache, converted to fp32 in shared memory (row stride R + 1); lane j scores key j of the tile, then lane l
+// accumulates output columns l, l + 32, ...  RI = ceil(R / 32) columns per lane.
+constexpr int LA_KT = 32;
+constexpr int LA_HPC = 8;  // heads per CTA
+
+template <typename TC, typename TQ, int RI>
+__global__ void __launch_bounds__(128)
+latent_attention_kernel(const TQ* __restrict__ q, long long q_tok_stride, long long q_head_stride, const TC* __restrict__ cache,
+                        float* __restrict__ out, long long o_tok_stride, long long o_head_stride, float* __restrict__ part_ml,
+                        float* __restrict__ part_acc, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                        const int* __restrict__ block_table, int bt_stride, int block_size, int H, int R, float scale, int n_splits) {
+  extern __shared__ float smem[];
+  const int t = blockIdx.x, split = blockIdx.y, hg = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int RS = R + 1;
+  float* q_s = smem;                       // [LA_HPC][R]
+  float* c_s = q_s + LA_HPC * R;           // [LA_KT][RS]
+  float* p_s = c_s + LA_KT * RS;           // [4][2][LA_KT]
+  const int seq = tok_seq[t], pos = tok_pos[t];
+  const int n_keys = pos + 1;
+  int chunk = (n_keys + n_splits - 1) / n_splits;
+  chunk = (chunk + LA_KT - 1) / LA_KT * LA_KT;
+  const int k0 = split * chunk, k1 = min(n_keys, k0 + chunk);
+  const int h_base = hg * LA_HPC;
+  for (int i = threadIdx.x; i < LA_HPC * R; i += blockDim.x) {
+    const int h = h_base + i / R, r = i % R;
+    q_s[i] = h < H ? to_f(q[t * q_tok_stride + h * q_head_stride + r]) * scale : 0.f;
+  }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float acc[2][RI];
+#pragma unroll
+  for (int a = 0; a < 2; ++a)
+#pragma unroll
+    for (int i = 0; i < RI; ++i) acc[a][i] = 0.f;
+  const int* bt = block_table + static_cast<size_t>(seq) * bt_stride;
+  for (int kt = k0; kt < k1; kt += LA_KT) {
+    __syncthreads();  // the previous tile is consumed (and q_s is written)
+    for (int i = threadIdx.x; i < LA_KT * R; i += blockDim.x) {
+      const int j = i / R, r = i % R;
+      const int k = kt + j;
+      float v = 0.f;
+      if (k < k1) {
+        const int blk = bt[k / block_size];
+        v = to_f(cache[(static_cast<size_t>(blk) * block_size + k % block_size) * R + r]);
+      }
+      c_s[j * RS + r] = v;
+    }
+    __syncthreads();
+    const bool valid = kt + lane < k1;
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+      const int hl = warp + 4 * a;
+      if (h_base + hl >= H) continue;  // warp-uniform
+      const float* qh = q_s + hl * R;
+      const float* cj = c_s + lane * RS;
+      float s = 0.f;
+      for (int r = 0; r < R; ++r) s = fmaf(qh[r], cj[r], s);
+      s = valid ? s : -INFINITY;
+      const float mn = fmaxf(m[a], warp_max(s));  // finite: every tile holds at least one visible key
+      const float p = valid ? expf(s - mn) : 0.f;
+      const float corr = expf(m[a] - mn);         // exp(-inf) = 0 on the first tile
+      l[a] = l[a] * corr + warp_sum(p);
+      m[a] = mn;
+      float* pw = p_s + (warp * 2 + a) * LA_KT;
+      pw[lane] = p;
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < RI; ++i) {
+        const int r = lane + 32 * i;
+        if (r < R) {
+          float o = acc[a][i] * corr;
+          for (int j = 0; j < LA_KT; ++j) o = fmaf(pw[j], c_s[j * RS + r], o);
+          acc[a][i] = o;
+        }
+      }
+      __syncwarp();
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < 2; ++a) {
+    const int h = h_base + warp + 4 * a;
+    if (h >= H) continue;
+    if (n_splits == 1) {
+      const float inv = 1.f / l[a];
+#pragma unroll
+      for (int i = 0; i < RI; ++i) {
+        const int r = lane + 32 * i;
+        if (r < R) out[t * o_tok_stride + h * o_head_stride + r] = acc[a][i] * inv;
+      }
+    } else {
+      const size_t slot = (static_cast<size_t>(t) * n_splits + split) * H + h;
+      if (lane == 0) {
+        part_ml[2 * slot] = m[a];
+        part_ml[2 * slot + 1] = l[a];
+      }
+#pragma unroll
+      for (int i = 0; i < RI; ++i) {
+        const int r = lane + 32 * i;
+        if (r < R) part_acc[slot * R + r] = acc[a][i];
+      }
+    }
+  }
+}
+
+// one warp per (token, head): combine the splits' (max, sum, unnormalised output)
+__global__ void latent_attention_merge_kernel(const float* __restrict__ part_ml, const float* __restrict__ part_acc, float* __restrict__ out,
+                                              long long o_tok_stride, long long o_head_stride, int n_tokens, int H, int R, int n_splits) {
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (gw >= n_tokens * H) return;
+  const int t = gw / H, h = gw % H;
+  float mx = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, part_ml[2 * ((static_cast<size_t>(t) * n_splits + s) * H + h)]);
+  float l = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const size_t slot = (static_cast<size_t>(t) * n_splits + s) * H + h;
+    const float ms = part_ml[2 * slot];
+    if (ms != -INFINITY) l += part_ml[2 * slot + 1] * expf(ms - mx);
+  }
+  const float inv = 1.f / l;
+  for (int r = lane; r < R; r += 32) {
+    float o = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const size_t slot = (static_cast<size_t>(t) * n_splits + s) * H + h;
+      const float ms = part_ml[2 * slot];
+      if (ms != -INFINITY) o = fmaf(part_acc[slot * R + r], expf(ms - mx), o);
+    }
+    out[t * o_tok_stride + h * o_head_stride + r] = o * inv;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------- elementwise
+template <typename T>
+__global__ void sigmoid_gate_mul_kernel(T* __restrict__ a, long long a_ld, const T* __restrict__ g, long long g_ld, int cols, long long n) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / cols;
+    const int c = static_cast<int>(i % cols);
+    const float gv = to_f(g[r * g_ld + c]);
+    a[r * a_ld + c] = from_f<T>(to_f(a[r * a_ld + c]) * (1.f / (1.f + expf(-gv))));
+  }
+}
+
+// gu [rows, 2 F] = (gate | up) -> out [rows, F]
+template <typename T>
+__global__ void clamped_swish_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int F, float alpha, float limit,
+                                          float shift) {
+  const long long n = rows * F;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / F;
+    const int c = static_cast<int>(i % F);
+    const float g = fminf(to_f(gu[r * 2 * F + c]), limit);
+    const float u = fminf(fmaxf(to_f(gu[r * 2 * F + F + c]), -limit), limit);
+    out[i] = from_f<T>(g * (1.f / (1.f + expf(-alpha * g))) * (u + shift));
+  }
+}
+
+__global__ void softcap_kernel(float* __restrict__ x, long long ld, int cols, long long n, float cap) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float* p = x + (i / cols) * ld + (i % cols);
+    *p = cap * tanhf(*p / cap);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------- router
+// One warp per token.  Shared memory per warp: E choice scores + G group scores.  Ties go to the lower index.
+__global__ void grouped_topk_gating_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int* __restrict__ expert_counts,
+                                           float* __restrict__ scores, int* __restrict__ assignments, int* __restrict__ offsets, int n_tokens,
+                                           int E, int K, int G, int keep, int normalize) {
+  extern __shared__ float smem[];
+  const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tok = blockIdx.x * (blockDim.x >> 5) + wib;
+  if (tok >= n_tokens) return;
+  float* choice = smem + static_cast<size_t>(wib) * (E + G);
+  float* gsc = choice + E;
+  const float* lg = logits + static_cast<size_t>(tok) * E;
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) sum += expf(lg[e] - mx);
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  for (int e = lane; e < E; e += 32) choice[e] = expf(lg[e] - mx) * inv + (correction ? correction[e] : 0.f);
+  __syncwarp();
+  if (G > 1 && keep < G) {
+    const int per = E / G;
+    for (int g = 0; g < G; ++g) {
+      float v = -INFINITY;
+      for (int e = lane; e < per; e += 32) v = fmaxf(v, choice[g * per + e]);
+      v = warp_max(v);
+      if (lane == 0) gsc[g] = v;
+    }
+    __syncwarp();
+    // the `keep` best groups survive: group g is dropped when at least `keep` groups beat it (higher score, or equal and lower index)
+    for (int g = 0; g < G; ++g) {
+      int better = 0;
+      const float mine = gsc[g];
+      for (int o = lane; o < G; o += 32) better += (gsc[o] > mine || (gsc[o] == mine && o < g)) ? 1 : 0;
+      better = static_cast<int>(warp_sum(static_cast<float>(better)) + 0.5f);
+      if (better >= keep)
+        for (int e = lane; e < per; e += 32) choice[g * per + e] = -INFINITY;
+      __syncwarp();
+    }
+  }
+  float top_sum = 0.f;
+  float my_score = 0.f;   // lane k keeps the k-th pick
+  int my_expert = -1;
+  for (int k = 0; k < K; ++k) {
+    float best = -INFINITY;
+    int best_e = -1;
+    for (int e = lane; e < E; e += 32) {
+      const float v = choice[e];
+      if (v > best || (best_e < 0 && v > -INFINITY)) { best = v; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (oe >= 0 && (best_e < 0 || ob > best || (ob == best && oe < best_e))) { best = ob; best_e = oe; }
+    }
+    float s = 0.f;
+    if (best_e >= 0) {
+      s = expf(lg[best_e] - mx) * inv;
+      if (lane == 0) choice[best_e] = -INFINITY;
+    }
+    __syncwarp();
+    top_sum += s;
+    if (lane == k) { my_score = s; my_expert = best_e; }
+  }
+  if (lane < K) {
+    const int e = my_expert >= 0 ? my_expert : 0;  // fewer selectable experts than K cannot happen for valid configurations
+    assignments[tok * K + lane] = e;
+    scores[tok * K + lane] = normalize ? my_score / top_sum : my_score;
+    offsets[tok * K + lane] = atomicAdd(&expert_counts[e], 1);
+  }
+}
+
+__global__ void expert_cumsum_kernel(const int* __restrict__ counts, long long* __restrict__ cumsum, int E) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    long long s = 0;
+    for (int e = 0; e < E; ++e) { s += counts[e]; cumsum[e] = s; }
+  }
+}
+
+template <typename T>
+__global__ void moe_scatter_kernel(const T* __restrict__ x, const int* __restrict__ assignments, const int* __restrict__ offsets,
+                                   const long long* __restrict__ cumsum, T* __restrict__ moe_in, int* __restrict__ mapped_slots, int dim, int K) {
+  const int t = blockIdx.x;
+  for (int k = 0; k < K; ++k) {
+    const int e = assignments[t * K + k];
+    const long long slot = (e == 0 ? 0 : cumsum[e - 1]) + offsets[t * K + k];
+    if (threadIdx.x == 0) mapped_slots[t * K + k] = static_cast<int>(slot);
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) moe_in[slot * dim + c] = x[static_cast<size_t>(t) * dim + c];
+  }
+}
+
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ moe_out, const float* __restrict__ scores, const int* __restrict__ mapped_slots,
+                                  float* __restrict__ out, int dim, int K) {
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < K; ++k) acc = fmaf(scores[t * K + k], to_f(moe_out[static_cast<size_t>(mapped_slots[t * K + k]) * dim + c]), acc);
+    out[static_cast<size_t>(t) * dim + c] = acc;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------- grouped GEMM on CUDA cores
+// out[r, n] = sum_k x[r, k] * w[e(r), n, k] for rows sorted by expert (inclusive row cumsum per expert on the device).
+// Tiles of 32 rows x 64 columns that never straddle experts; tile b of the grid is located by walking the cumsum.
+constexpr int GM = 32, GN = 64, GK = 16;
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_gemm_rows_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ out, const long long* __restrict__ cumsum, int E,
+                     int N, int K) {
+  __shared__ float xs[GK][GM + 1];
+  __shared__ float ws[GK][GN + 1];
+  __shared__ int s_info[3];
+  if (threadIdx.x == 0) {
+    int b = blockIdx.x, e = 0;
+    long long start = 0;
+    s_info[0] = -1;
+    for (; e < E; ++e) {
+      const long long end = cumsum[e];
+      const int tiles = static_cast<int>((end - start + GM - 1) / GM);
+      if (b < tiles) {
+        s_info[0] = e;
+        s_info[1] = static_cast<int>(start) + b * GM;
+        s_info[2] = static_cast<int>(end);
+        break;
+      }
+      b -= tiles;
+      start = end;
+    }
+  }
+  __syncthreads();
+  const int e = s_info[0];
+  if (e < 0) return;
+  const int r0 = s_info[1], r_end = s_info[2], n0 = blockIdx.y * GN;
+  const T* we = w + static_cast<size_t>(e) * N * K;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;  // thread computes rows ty*2 .. +1, columns tx*4 .. +3
+  float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  for (int k0 = 0; k0 < K; k0 += GK) {
+    for (int i = threadIdx.x; i < GM * GK; i += 256) {
+      const int r = i / GK, k = i % GK;
+      xs[k][r] = (r0 + r < r_end && k0 + k < K) ? to_f(x[static_cast<size_t>(r0 + r) * K + k0 + k]) : 0.f;
+    }
+    for (int i = threadIdx.x; i < GN * GK; i += 256) {
+      const int n = i / GK, k = i % GK;
+      ws[k][n] = (n0 + n < N && k0 + k < K) ? to_f(we[static_cast<size_t>(n0 + n) * K + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < GK; ++k) {
+      const float a0 = xs[k][ty * 2], a1 = xs[k][ty * 2 + 1];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float b = ws[k][tx * 4 + j];
+        acc[0][j] = fmaf(a0, b, acc[0][j]);
+        acc[1][j] = fmaf(a1, b, acc[1][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = r0 + ty * 2 + i;
+    if (r >= r_end) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) out[static_cast<size_t>(r) * N + n] = from_f<T>(acc[i][j]);
+    }
+  }
+}
+
+}  // namespace latent
+}  // namespace dsb
+
+using namespace dsb;
+using namespace dsb::latent;
+
+static inline int grid_for(long long n, int block) {
+  long long g = (n + block - 1) / block;
+  return static_cast<int>(g < 1 ? 1 : (g > 148 * 16 ? 148 * 16 : g));
+}
+
+// out[t, :] = table[ids[t], :] + sinusoid(tok_pos[t]): entry 2i = sin(p f_i), entry 2i + 1 = cos(p f_i); `freq` holds the
+// ceil(dim / 2) frequencies as doubles on the device.  table_dtype: 0 = bf16, 1 = fp32.  out is fp32.
+DSB_EXPORT int dsb200_embed_sinusoid(const long long* ids, const void* table, int table_dtype, const int* tok_pos, const double* freq,
+                                     float* out, int n_tokens, int dim, cudaStream_t stream) {
+  if (n_tokens == 0) return DSB_OK;
+  if (table_dtype == 0)
+    embed_sinusoid_kernel<bf16><<<n_tokens, 128, 0, stream>>>(ids, (const bf16*)table, tok_pos, freq, out, dim);
+  else
+    embed_sinusoid_kernel<float><<<n_tokens, 128, 0, stream>>>(ids, (const float*)table, tok_pos, freq, out, dim);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// Per row of the fp32 residual x [n_rows, dim] (row rows[r] when `rows` is given): if y: x += rms_norm(y) * (wb + ob); if w:
+// out = rms_norm(x) * (w + o).  y and out are bf16 (dtype 0) or fp32 (dtype 1); the weights are fp32.
+DSB_EXPORT int dsb200_sandwich_norm(float* x, const void* y, int y_dtype, const float* wb, float ob, const float* w, float o, void* out,
+                                    int out_dtype, const int* rows, int n_rows, int dim, float eps, cudaStream_t stream) {
+  if (n_rows == 0) return DSB_OK;
+  DSB_REQUIRE(y == nullptr || (wb != nullptr && rows == nullptr), "sandwich_norm: a branch needs its weight and cannot be combined with a row gather");
+  DSB_REQUIRE(w == nullptr || out != nullptr, "sandwich_norm: an output norm needs an output");
+  const int block = dim >= 1024 ? 256 : 128;
+#define LAUNCH(TY, TO) sandwich_norm_kernel<TY, TO><<<n_rows, block, 0, stream>>>(x, (const TY*)y, wb, ob, w, o, (TO*)out, rows, dim, eps)
+  if (y_dtype == 0 && out_dtype == 0) LAUNCH(bf16, bf16);
+  else if (y_dtype == 0) LAUNCH(bf16, float);
+  else if (out_dtype == 0) LAUNCH(float, bf16);
+  else LAUNCH(float, float);
+#undef LAUNCH
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// lat [n_tokens, ld] holds (query latent [nq] | key/value latent [nkv]) of every token.  cq [n_tokens, nq] = plain-weight RMS norm
+// of the first part; the RMS-normed second part is written to the token's row of cache [blocks, block_size, nkv].
+DSB_EXPORT int dsb200_latent_norm_append(const void* lat, int ld, const float* wq, const float* wkv, void* cq, void* cache, const int* tok_seq,
+                                         const int* tok_pos, const int* block_table, int bt_stride, int block_size, int n_tokens, int nq,
+                                         int nkv, float eps, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return DSB_OK;
+  const int warps = 2 * n_tokens, wpb = 4;
+  const int grid = (warps + wpb - 1) / wpb;
+  if (dtype == 0)
+    latent_norm_append_kernel<bf16><<<grid, wpb * 32, 0, stream>>>((const bf16*)lat, ld, wq, wkv, (bf16*)cq, (bf16*)cache, tok_seq, tok_pos,
+                                                                  block_table, bt_stride, block_size, n_tokens, nq, nkv, eps);
+  else
+    latent_norm_append_kernel<float><<<grid, wpb * 32, 0, stream>>>((const float*)lat, ld, wq, wkv, (float*)cq, (float*)cache, tok_seq, tok_pos,
+                                                                   block_table, bt_stride, block_size, n_tokens, nq, nkv, eps);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// floats of scratch `dsb200_latent_attention` needs for n_splits > 1
+DSB_EXPORT long long dsb200_latent_attention_scratch_floats(int n_tokens, int H, int R, int n_splits) {
+  return n_splits > 1 ? static_cast<long long>(n_tokens) * n_splits * H * (R + 2) : 0;
+}
+
+// out[t, h, :] = sum_j softmax_j(scale * q[t, h, :] . c_j) c_j over the cached latents c_0 .. c_pos(t) of the token's sequence.
+// q: bf16 / fp32 (q_dtype 0 / 1) with element strides per token and head; cache [blocks, block_size, R] bf16 / fp32 (cache_dtype);
+// out fp32 with element strides per token and head.  R <= 512.
+DSB_EXPORT int dsb200_latent_attention(const void* q, int q_dtype, long long q_tok_stride, long long q_head_stride, const void* cache,
+                                       int cache_dtype, float* out, long long o_tok_stride, long long o_head_stride, float* scratch,
+                                       const int* tok_seq, const int* tok_pos, const int* block_table, int bt_stride, int block_size,
+                                       int n_tokens, int H, int R, float scale, int n_splits, cudaStream_t stream) {
+  if (n_tokens == 0) return DSB_OK;
+  DSB_REQUIRE(R >= 1 && R <= 512 && H >= 1 && n_splits >= 1, "latent_attention: R=%d (1..512) H=%d splits=%d", R, H, n_splits);
+  DSB_REQUIRE(n_splits == 1 || scratch != nullptr, "latent_attention: splits need scratch");
+  float* part_ml = scratch;
+  float* part_acc = scratch ? scratch + static_cast<size_t>(n_tokens) * n_splits * H * 2 : nullptr;
+  const dim3 grid(n_tokens, n_splits, (H + LA_HPC - 1) / LA_HPC);
+  const size_t smem = (static_cast<size_t>(LA_HPC) * R + LA_KT * (R + 1) + 4 * 2 * LA_KT) * sizeof(float);
+#define LAUNCH(TC, TQ, RI)                                                                                                        \
+  do {                                                                                                                            \
+    auto kern = latent_attention_kernel<TC, TQ, RI>;                                                                              \
+    if (smem > 48 * 1024) DSB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));     \
+    kern<<<grid, 128, smem, stream>>>((const TQ*)q, q_tok_stride, q_head_stride, (const TC*)cache, out, o_tok_stride, o_head_stride, \
+                                      part_ml, part_acc, tok_seq, tok_pos, block_table, bt_stride, block_size, H, R, scale, n_splits); \
+  } while (0)
+#define BY_RI(TC, TQ)                          \
+  do {                                         \
+    if (R <= 32) LAUNCH(TC, TQ, 1);            \
+    else if (R <= 64) LAUNCH(TC, TQ, 2);       \
+    else if (R <= 128) LAUNCH(TC, TQ, 4);      \
+    else if (R <= 256) LAUNCH(TC, TQ, 8);      \
+    else LAUNCH(TC, TQ, 16);                   \
+  } while (0)
+  if (cache_dtype == 0 && q_dtype == 0) BY_RI(bf16, bf16);
+  else if (cache_dtype == 0) BY_RI(bf16, float);
+  else if (q_dtype == 0) BY_RI(float, bf16);
+  else BY_RI(float, float);
+#undef BY_RI
+#undef LAUNCH
+  DSB_CHECK_CUDA(cudaGetLastError());
+  if (n_splits > 1) {
+    const long long warps = static_cast<long long>(n_tokens) * H;
+    latent_attention_merge_kernel<<<static_cast<int>((warps + 3) / 4), 128, 0, stream>>>(part_ml, part_acc, out, o_tok_stride, o_head_stride,
+                                                                                         n_tokens, H, R, n_splits);
+    DSB_CHECK_CUDA(cudaGetLastError());
+  }
+  return DSB_OK;
+}
+
+// a[r, c] *= sigmoid(g[r, c]) over [rows, cols] with row strides (elements).  dtype 0 = bf16, 1 = fp32.
+DSB_EXPORT int dsb200_sigmoid_gate_mul(void* a, long long a_ld, const void* g, long long g_ld, long long rows, int cols, int dtype,
+                                       cudaStream_t stream) {
+  const long long n = rows * cols;
+  if (n == 0) return DSB_OK;
+  if (dtype == 0)
+    sigmoid_gate_mul_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((bf16*)a, a_ld, (const bf16*)g, g_ld, cols, n);
+  else
+    sigmoid_gate_mul_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>((float*)a, a_ld, (const float*)g, g_ld, cols, n);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// gu [rows, 2 F] = (gate | up) -> out [rows, F] = g' * sigmoid(alpha g') * (clamp(u, -limit, limit) + shift), g' = min(g, limit)
+DSB_EXPORT int dsb200_clamped_swish_gate(const void* gu, void* out, long long rows, int F, float alpha, float limit, float shift, int dtype,
+                                         cudaStream_t stream) {
+  const long long n = rows * F;
+  if (n == 0) return DSB_OK;
+  if (dtype == 0)
+    clamped_swish_gate_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((const bf16*)gu, (bf16*)out, rows, F, alpha, limit, shift);
+  else
+    clamped_swish_gate_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>((const float*)gu, (float*)out, rows, F, alpha, limit, shift);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// x[r, c] = cap * tanh(x[r, c] / cap) over fp32 [rows, cols] with row stride ld
+DSB_EXPORT int dsb200_softcap(float* x, long long ld, long long rows, int cols, float cap, cudaStream_t stream) {
+  const long long n = rows * cols;
+  if (n == 0) return DSB_OK;
+  softcap_kernel<<<grid_for(n, 256), 256, 0, stream>>>(x, ld, cols, n, cap);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// Router: softmax over the E logits of a token; choice score = score + correction[e] (correction may be null); experts are split
+// into `groups` equal neighbour groups, of which the `keep` with the largest maximal choice score stay selectable; the top_k
+// selectable experts by choice score are assigned; their weights are the uncorrected scores (divided by their sum when
+// `normalize`).  Outputs as dsb200_top_k_gating; expert_counts must be zeroed by the caller.
+DSB_EXPORT int dsb200_grouped_topk_gating(const float* logits, const float* correction, int* expert_counts, float* scores, int* assignments,
+                                          int* offsets, int n_tokens, int n_experts, int top_k, int groups, int keep, int normalize,
+                                          cudaStream_t stream) {
+  if (n_tokens == 0) return DSB_OK;
+  DSB_REQUIRE(top_k >= 1 && top_k <= 32 && top_k <= n_experts && n_experts <= 2048, "grouped_topk_gating: k=%d (1..32), experts=%d (<=2048)",
+              top_k, n_experts);
+  DSB_REQUIRE(groups >= 1 && n_experts % groups == 0 && keep >= 1 && keep <= groups && keep * (n_experts / groups) >= top_k,
+              "grouped_topk_gating: %d experts in %d groups, %d kept, top %d", n_experts, groups, keep, top_k);
+  const int wpb = 4;
+  const size_t smem = static_cast<size_t>(wpb) * (n_experts + groups) * sizeof(float);
+  grouped_topk_gating_kernel<<<(n_tokens + wpb - 1) / wpb, wpb * 32, smem, stream>>>(logits, correction, expert_counts, scores, assignments,
+                                                                                   offsets, n_tokens, n_experts, top_k, groups, keep, normalize);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// Rows of x [n_tokens, dim] copied into expert-sorted order (any dim; dtype 0 = bf16, 1 = fp32); also writes the inclusive
+// per-expert row cumsum and every (token, k)'s row.
+DSB_EXPORT int dsb200_moe_scatter_rows(const void* x, const int* expert_counts, const int* assignments, const int* offsets,
+                                       long long* expert_cumsum, void* moe_in, int* mapped_slots, int n_tokens, int n_experts, int dim,
+                                       int top_k, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return DSB_OK;
+  expert_cumsum_kernel<<<1, 32, 0, stream>>>(expert_counts, expert_cumsum, n_experts);
+  if (dtype == 0)
+    moe_scatter_kernel<bf16><<<n_tokens, 128, 0, stream>>>((const bf16*)x, assignments, offsets, expert_cumsum, (bf16*)moe_in, mapped_slots, dim, top_k);
+  else
+    moe_scatter_kernel<float><<<n_tokens, 128, 0, stream>>>((const float*)x, assignments, offsets, expert_cumsum, (float*)moe_in, mapped_slots, dim,
+                                                           top_k);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// out[t, :] (fp32) = sum_k scores[t, k] * moe_out[mapped_slots[t, k], :]
+DSB_EXPORT int dsb200_moe_gather_rows(const void* moe_out, const float* scores, const int* mapped_slots, float* out, int n_tokens, int dim,
+                                      int top_k, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return DSB_OK;
+  if (dtype == 0)
+    moe_gather_kernel<bf16><<<n_tokens, 128, 0, stream>>>((const bf16*)moe_out, scores, mapped_slots, out, dim, top_k);
+  else
+    moe_gather_kernel<float><<<n_tokens, 128, 0, stream>>>((const float*)moe_out, scores, mapped_slots, out, dim, top_k);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// Grouped expert GEMM on CUDA cores: out[r, :] = w[expert(r)] x[r, :] for the R rows sorted by expert; x [R, K], w [E, N, K],
+// out [R, N], all bf16 (dtype 0) or all fp32 (dtype 1), contiguous; fp32 accumulation.  expert_cumsum [E] int64 on the device.
+DSB_EXPORT int dsb200_moe_gemm_rows(const void* x, const void* w, void* out, const long long* expert_cumsum, int R, int N, int K, int E,
+                                    int dtype, cudaStream_t stream) {
+  if (R == 0) return DSB_OK;
+  const dim3 grid((R + GM - 1) / GM + E, (N + GN - 1) / GN);
+  if (dtype == 0)
+    moe_gemm_rows_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)x, (const bf16*)w, (bf16*)out, expert_cumsum, E, N, K);
+  else
+    moe_gemm_rows_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, (const float*)w, (float*)out, expert_cumsum, E, N, K);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}

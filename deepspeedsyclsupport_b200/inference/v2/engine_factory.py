@@ -30,13 +30,23 @@ def build_engine_from_state_dict(model_type, hf_config: dict, state_dict: dict, 
     return InferenceEngineV2(builder, engine_config)
 
 
-def build_hf_engine(path: str, engine_config: RaggedInferenceEngineConfig, debug_level: int = 20):
+def model_type_of(model_config: dict) -> str:
+    """Key of the family policy: HF's `model_type`, or the lower-cased `architecture` of configs that name their design that way."""
+    t = model_config.get("model_type") or model_config.get("architecture")
+    if not t:
+        raise ValueError("config.json names neither a model_type nor an architecture")
+    return str(t).lower()
+
+
+def build_hf_engine(path: str, engine_config: RaggedInferenceEngineConfig, debug_level: int = 20, dtype=None):
+    """`dtype`: activation / weight dtype of the engine; None takes `torch_dtype` of the checkpoint's config (bf16 when absent)."""
     if os.path.exists(os.path.join(path, "ds_model_config.pkl")):
         return build_engine_from_ds_checkpoint(path, engine_config, debug_level=debug_level)
     ck = HuggingFaceCheckpointEngine(path)
-    model_type = ck.model_config["model_type"]
+    model_type = model_type_of(ck.model_config)
     policy_for(model_type)
-    dtype = {"float16": torch.float16, "float32": torch.float32}.get(str(ck.model_config.get("torch_dtype", "bfloat16")), torch.bfloat16)
+    if dtype is None:
+        dtype = {"float16": torch.float16, "float32": torch.float32}.get(str(ck.model_config.get("torch_dtype", "bfloat16")), torch.bfloat16)
 
     def builder(tp_group, device):
         # the checkpoint is streamed: every tensor is sharded and moved as soon as its parameter is complete

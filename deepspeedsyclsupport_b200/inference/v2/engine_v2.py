@@ -30,8 +30,11 @@ class InferenceEngineV2:
         self._model = model_builder(self._tp_group, self.device)
         spec = self._model.spec
         block = int(getattr(engine_config.state_manager, "kv_block_size", 0) or 0) or (128 if self.device.type == "cuda" else 16)
-        kv_cfg = KVCacheConfig(block_size=block,
-                               cache_shape=(spec.num_layers, self._model.hkv, spec.head_dim), cache_dtype="bf16")
+        if hasattr(self._model, "kv_cache_config"):  # models whose cached layers differ from (key, value) x heads describe them
+            kv_cfg = self._model.kv_cache_config(block_size=block)
+        else:
+            kv_cfg = KVCacheConfig(block_size=block,
+                                   cache_shape=(spec.num_layers, self._model.hkv, spec.head_dim), cache_dtype="bf16")
         self._state_manager = DSStateManager(engine_config.state_manager, kv_cfg, base_mp_group=self._tp_group)
         self._batch = RaggedBatchWrapper(engine_config.state_manager)
         self._batch.set_block_table_shape(self._state_manager.max_blocks_per_seq)
@@ -57,9 +60,11 @@ class InferenceEngineV2:
     def model(self):
         return self._model
 
-    def put(self, batch_uids: Iterable[int], batch_tokens: Iterable[torch.Tensor], do_checks: bool = True) -> torch.Tensor:
+    def put(self, batch_uids: Iterable[int], batch_tokens: Iterable[torch.Tensor], do_checks: bool = True,
+            logit_positions=None) -> torch.Tensor:
         """Run one ragged forward over `batch_tokens[i]` new tokens of sequence `batch_uids[i]`; returns logits
-        [n_seqs, vocab] of the last token of every sequence."""
+        [n_seqs, vocab] of the last token of every sequence -- or, with `logit_positions` (one list per sequence of indices
+        into that sequence's tokens of this call, possibly empty), [wanted positions, vocab] in the order given."""
         batch_uids, batch_tokens = list(batch_uids), list(batch_tokens)
         if do_checks:
             token_lens = [t.numel() for t in batch_tokens]
@@ -76,6 +81,8 @@ class InferenceEngineV2:
             seq.pre_forward(tokens.numel())
             self._batch.insert_sequence(seq, tokens.reshape(-1), do_checks=do_checks)
             descs.append(seq)
+        if logit_positions is not None:
+            self._batch.set_logit_positions(list(logit_positions))
         self._batch.finalize()
         with torch.no_grad():
             run = getattr(self._model, "forward_graphed", self._model.forward)  # decode steps replay a CUDA graph

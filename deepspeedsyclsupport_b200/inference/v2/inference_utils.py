@@ -37,13 +37,15 @@ class ActivationType(IntEnum):
     ReGLU = 4
     SiGLU = 5
     IDENTITY = 6
+    ClampedSwiGLU = 7  # gated: min(g, L) * sigmoid(alpha min(g, L)) * (clamp(u, -L, L) + shift); alpha, L, shift from the module config
     InvalidType = -1
 
 
-_GATED = (ActivationType.GEGLU, ActivationType.ReGLU, ActivationType.SiGLU)
+_GATED = (ActivationType.GEGLU, ActivationType.ReGLU, ActivationType.SiGLU, ActivationType.ClampedSwiGLU)
 # name understood by ops/fused_ops (bias_act / gated_act)
 _ACT_NAME = {ActivationType.GELU: "gelu", ActivationType.RELU: "relu", ActivationType.SILU: "silu", ActivationType.GEGLU: "gelu",
-             ActivationType.ReGLU: "relu", ActivationType.SiGLU: "silu", ActivationType.IDENTITY: "identity"}
+             ActivationType.ReGLU: "relu", ActivationType.SiGLU: "silu", ActivationType.IDENTITY: "identity",
+             ActivationType.ClampedSwiGLU: "clamped_swiglu"}
 
 
 def is_gated(act_fn) -> bool:

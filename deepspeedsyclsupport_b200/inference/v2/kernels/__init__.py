@@ -221,3 +221,175 @@ def moe_gather(moe_out, scores, mapped_slots):
                                         native.stream_ptr())
     native.check(rc)
     return out
+
+
+# ---- kernels of csrc/ragged/latent_ops.cu: fp32 residual stream, latent-cache attention, grouped top-k router, expert MLP pieces
+# for any width in bf16 or fp32.  Device only: these ops have no host form (their oracles live with the tests).
+native.register_sigs({
+    "dsb200_embed_sinusoid": "pp i pp p ii p",
+    "dsb200_sandwich_norm": "pp i p f p f p i p ii f p",
+    "dsb200_latent_norm_append": "p i pp pp ppp iii ii f i p",
+    "dsb200_latent_attention_scratch_floats": "iiii",
+    "dsb200_latent_attention": "p i ll p i p ll p ppp ii iii f i p",
+    "dsb200_sigmoid_gate_mul": "p l p l l i i p",
+    "dsb200_clamped_swish_gate": "pp l i fff i p",
+    "dsb200_softcap": "p l l i f p",
+    "dsb200_grouped_topk_gating": "pppppp iiiiii p",
+    "dsb200_moe_scatter_rows": "ppppppp iiii i p",
+    "dsb200_moe_gather_rows": "pppp iii i p",
+    "dsb200_moe_gemm_rows": "pppp iiii i p",
+}, restype_long=("dsb200_latent_attention_scratch_floats", ))
+
+_DT = {torch.bfloat16: 0, torch.float32: 1}
+
+
+def _dt(t):
+    if not t.is_cuda or t.dtype not in _DT:
+        raise native.NativeError(f"this op runs on CUDA tensors of bf16 or fp32 (got {t.dtype} on {t.device})")
+    return _DT[t.dtype]
+
+
+def sinusoid_frequencies(dim, base=10000.0, device=None):
+    """f_i = base ** (-2 i / dim), i < ceil(dim / 2), in float64 (positions times these are taken in double on the device)."""
+    i = torch.arange((dim + 1) // 2, dtype=torch.float64)
+    return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / dim).to(device)
+
+
+def embed_sinusoid(ids, table, tok_pos, freq):
+    """fp32 [T, dim]: table[ids] + (sin(p f_0), cos(p f_0), sin(p f_1), ...)."""
+    T, dim = ids.numel(), table.shape[1]
+    out = torch.empty(T, dim, dtype=torch.float32, device=table.device)
+    native.check(native.lib().dsb200_embed_sinusoid(native.ptr(ids), native.ptr(table), _dt(table), native.ptr(tok_pos), native.ptr(freq),
+                                                    native.ptr(out), T, dim, native.stream_ptr()))
+    return out
+
+
+def sandwich_norm(x, y=None, wb=None, ob=0.0, w=None, o=0.0, eps=1e-6, out_dtype=torch.bfloat16, rows=None):
+    """On the fp32 residual x [T, dim], in place: x += rms_norm(y) * (wb + ob) when a branch output y is given; returns
+    rms_norm(x) * (w + o) in `out_dtype` when w is given (else None).  `rows` (int32 indices): normalise only those rows of x
+    (no branch then); the result has one row per index."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.is_cuda
+    n = x.shape[0] if rows is None else rows.numel()
+    out = torch.empty(n, x.shape[1], dtype=out_dtype, device=x.device) if w is not None else None
+    if y is not None:
+        assert y.is_contiguous() and y.shape == x.shape
+    native.check(native.lib().dsb200_sandwich_norm(native.ptr(x), native.ptr(y), _dt(y) if y is not None else 0, native.ptr(wb), float(ob),
+                                                   native.ptr(w), float(o), native.ptr(out), _DT[out_dtype], native.ptr(rows), n, x.shape[1],
+                                                   float(eps), native.stream_ptr()))
+    return out
+
+
+def latent_norm_append(lat, wq, wkv, cache, tok_seq, tok_pos, block_table, nq, nkv, eps):
+    """lat [T, >= nq + nkv]: rows (query latent | key/value latent).  Returns the RMS-normed query latents [T, nq]; the RMS-normed
+    key/value latent of every token is written into cache [blocks, block_size, nkv] at the token's position."""
+    T = lat.shape[0]
+    assert lat.stride(1) == 1 and cache.dtype == lat.dtype and cache.is_contiguous() and cache.shape[2] == nkv
+    cq = torch.empty(T, nq, dtype=lat.dtype, device=lat.device)
+    native.check(native.lib().dsb200_latent_norm_append(native.ptr(lat), lat.stride(0), native.ptr(wq), native.ptr(wkv), native.ptr(cq),
+                                                        native.ptr(cache), native.ptr(tok_seq), native.ptr(tok_pos), native.ptr(block_table),
+                                                        block_table.stride(0), cache.shape[1], T, nq, nkv, float(eps), _dt(lat),
+                                                        native.stream_ptr()))
+    return cq
+
+
+def _latent_splits(T, head_groups, max_keys):
+    """Key splits per token: fill the SMs when the batch is small and the context long; one split per 512 keys at most."""
+    ctas = max(1, T * head_groups)
+    return max(1, min(-(-max_keys // 512), (2 * 148) // ctas, 32))
+
+
+def latent_attention(q_abs, cache, tok_seq, tok_pos, block_table, scale, out=None, max_keys=None, n_splits=None):
+    """q_abs [T, H, R] (any strides with unit stride in R; bf16 / fp32): queries already mapped into the latent space.
+    cache [blocks, block_size, R].  Returns fp32 [T, H, R] (or fills `out`, any token / head strides):
+    sum_j softmax_j(scale q . c_j) c_j over the latents 0 .. pos(t) of the token's sequence."""
+    T, H, R = q_abs.shape
+    assert q_abs.stride(2) == 1 and cache.is_contiguous() and cache.shape[2] == R
+    if out is None:
+        out = torch.empty(T, H, R, dtype=torch.float32, device=q_abs.device)
+    assert out.dtype == torch.float32 and out.stride(2) == 1
+    if n_splits is None:
+        n_splits = _latent_splits(T, -(-H // 8), max_keys if max_keys is not None else block_table.shape[1] * cache.shape[1])
+    nf = native.lib().dsb200_latent_attention_scratch_floats(T, H, R, n_splits)
+    scratch = torch.empty(nf, dtype=torch.float32, device=q_abs.device) if nf else None
+    native.check(native.lib().dsb200_latent_attention(native.ptr(q_abs), _dt(q_abs), q_abs.stride(0), q_abs.stride(1), native.ptr(cache),
+                                                      _dt(cache), native.ptr(out), out.stride(0), out.stride(1), native.ptr(scratch),
+                                                      native.ptr(tok_seq), native.ptr(tok_pos), native.ptr(block_table), block_table.stride(0),
+                                                      cache.shape[1], T, H, R, float(scale), int(n_splits), native.stream_ptr()),
+                 2 if n_splits > 1 else 1)
+    return out
+
+
+def sigmoid_gate_mul(a, g):
+    """a *= sigmoid(g), in place; a and g are [rows, cols] views with unit column stride."""
+    assert a.shape == g.shape and a.dim() == 2 and a.stride(1) == 1 and g.stride(1) == 1 and a.dtype == g.dtype
+    native.check(native.lib().dsb200_sigmoid_gate_mul(native.ptr(a), a.stride(0), native.ptr(g), g.stride(0), a.shape[0], a.shape[1], _dt(a),
+                                                      native.stream_ptr()))
+    return a
+
+
+def clamped_swish_gate(gu, alpha, limit, shift):
+    """gu [rows, 2F] = (gate | up) -> [rows, F]: g' sigmoid(alpha g') (clamp(u, -limit, limit) + shift) with g' = min(g, limit)."""
+    assert gu.is_contiguous() and gu.shape[1] % 2 == 0
+    F = gu.shape[1] // 2
+    out = torch.empty(gu.shape[0], F, dtype=gu.dtype, device=gu.device)
+    native.check(native.lib().dsb200_clamped_swish_gate(native.ptr(gu), native.ptr(out), gu.shape[0], F, float(alpha), float(limit),
+                                                        float(shift), _dt(gu), native.stream_ptr()))
+    return out
+
+
+def softcap_(logits, cap):
+    """logits <- cap * tanh(logits / cap), in place on an fp32 [rows, cols] view."""
+    assert logits.dtype == torch.float32 and logits.is_cuda and logits.stride(1) == 1
+    native.check(native.lib().dsb200_softcap(native.ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], float(cap),
+                                             native.stream_ptr()))
+    return logits
+
+
+def grouped_topk_gating(logits, k, correction=None, groups=1, keep=1, normalize=False):
+    """Router with a choice correction and neighbour groups (see csrc/ragged/latent_ops.cu).  logits [T, E] fp32 ->
+    (expert_counts [E] int32, scores [T, k] fp32, assignments [T, k] int32, offsets [T, k] int32), as `top_k_gating`."""
+    assert logits.dtype == torch.float32 and logits.is_cuda and logits.is_contiguous()
+    T, E = logits.shape
+    counts = torch.zeros(E, dtype=torch.int32, device=logits.device)
+    scores = torch.empty(T, k, dtype=torch.float32, device=logits.device)
+    asg = torch.empty(T, k, dtype=torch.int32, device=logits.device)
+    off = torch.empty(T, k, dtype=torch.int32, device=logits.device)
+    native.check(native.lib().dsb200_grouped_topk_gating(native.ptr(logits), native.ptr(correction), native.ptr(counts), native.ptr(scores),
+                                                         native.ptr(asg), native.ptr(off), T, E, k, groups, keep, int(normalize),
+                                                         native.stream_ptr()))
+    return counts, scores, asg, off
+
+
+def moe_scatter_rows(x, counts, assignments, offsets):
+    """`moe_scatter` for any width and bf16 / fp32 rows."""
+    T, dim = x.shape
+    k, E = assignments.shape[1], counts.numel()
+    assert x.is_contiguous()
+    moe_in = torch.empty(T * k, dim, dtype=x.dtype, device=x.device)
+    cumsum = torch.empty(E, dtype=torch.int64, device=x.device)
+    slots = torch.empty(T, k, dtype=torch.int32, device=x.device)
+    native.check(native.lib().dsb200_moe_scatter_rows(native.ptr(x), native.ptr(counts), native.ptr(assignments), native.ptr(offsets),
+                                                      native.ptr(cumsum), native.ptr(moe_in), native.ptr(slots), T, E, dim, k, _dt(x),
+                                                      native.stream_ptr()), 2)
+    return moe_in, cumsum, slots
+
+
+def moe_gather_rows(moe_out, scores, mapped_slots):
+    """fp32 [T, dim]: sum_k scores[t, k] * moe_out[mapped_slots[t, k]]."""
+    T, k = mapped_slots.shape
+    assert moe_out.is_contiguous()
+    out = torch.empty(T, moe_out.shape[1], dtype=torch.float32, device=moe_out.device)
+    native.check(native.lib().dsb200_moe_gather_rows(native.ptr(moe_out), native.ptr(scores), native.ptr(mapped_slots), native.ptr(out), T,
+                                                     moe_out.shape[1], k, _dt(moe_out), native.stream_ptr()))
+    return out
+
+
+def moe_gemm_rows(x, w, cumsum):
+    """Grouped expert GEMM on CUDA cores (bf16 or fp32, fp32 accumulation, any shape): out[r] = w[expert(r)] @ x[r]."""
+    assert x.is_contiguous() and w.is_contiguous() and x.dtype == w.dtype and x.shape[1] == w.shape[2]
+    R, K = x.shape
+    E, N, _ = w.shape
+    out = torch.empty(R, N, dtype=x.dtype, device=x.device)
+    native.check(native.lib().dsb200_moe_gemm_rows(native.ptr(x), native.ptr(w), native.ptr(out), native.ptr(cumsum), R, N, K, E, _dt(x),
+                                                   native.stream_ptr()))
+    return out

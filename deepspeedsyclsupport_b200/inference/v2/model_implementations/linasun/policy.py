@@ -1,0 +1,32 @@
+"""Policy of the Linasun family: config.json with "architecture": "Linasun"; layer tensors live under `l<i>.`."""
+import re
+
+from ..inference_policy_base import ContainerMap, InferenceV2Policy
+from .container import LinasunNonTransformerContainer, LinasunTransformerContainer
+from .model import LinasunInferenceModel, LinasunSpec
+
+
+class _LinasunMap(ContainerMap):
+    """Layer tensors are named `l<i>.<rest>` (no dot between the prefix and the index)."""
+
+    def set_transformer_params(self, prefixes, containers) -> None:
+        self._prefix, self._transformer = "l", containers
+        self._rx = re.compile(r"^l(\d+)\.(.*)$")
+
+
+class LinasunPolicy(InferenceV2Policy):
+    model_types = ("linasun", )
+
+    def spec(self) -> LinasunSpec:
+        return LinasunSpec.from_config(self._model_config)
+
+    def instantiate_model(self, engine_config, mp_group, device=None):
+        return LinasunInferenceModel(self.spec(), tp_group=mp_group, dtype=self._dtype, device=device, engine_config=engine_config,
+                                     layer_container_cls=LinasunTransformerContainer,
+                                     non_transformer_container_cls=LinasunNonTransformerContainer)
+
+    def build_container_map(self) -> ContainerMap:
+        cmap = _LinasunMap()
+        cmap.set_transformer_params("l", self.model.layers)
+        cmap.set_non_transformer_params(self.model.non_transformer)
+        return cmap

@@ -205,6 +205,20 @@ class RaggedTransformer:
 
     def __init__(self, spec: ArchSpec, state_dict=None, tp_group=None, dtype=torch.bfloat16, device=None, symm=None, quantization_mode="",
                  engine_config=None, layer_container_cls=None, non_transformer_container_cls=None):
+        self._init_plumbing(spec, tp_group, dtype, device, engine_config, symm, quantization_mode)
+        s = spec
+        assert s.num_heads % self.tp == 0, "num_heads must be divisible by tp_size"
+        self.hq, self.hkv = sharding.get_local_heads(self.rank, self.tp, s.num_heads, s.num_kv_heads)
+        self.kv_replicated = s.num_kv_heads < self.tp
+        self.vocab_padded = -(-s.vocab_size // self.tp) * self.tp
+        self._build_modules()
+        self.layers = [(layer_container_cls or layer_container_class(s))(self) for _ in range(s.num_layers)]
+        self.non_transformer = (non_transformer_container_cls or NonTransformerContainer)(self)
+        if state_dict is not None:
+            self.load_canonical(state_dict)
+
+    def _init_plumbing(self, spec, tp_group, dtype, device, engine_config, symm=None, quantization_mode=""):
+        """What every family needs whatever its layers look like: the tensor-parallel group, dtype / device, the decode-graph cache."""
         self.spec = spec
         self.quantization_mode = quantization_mode or ""
         self.engine_config = engine_config
@@ -216,16 +230,6 @@ class RaggedTransformer:
         self.dtype = dtype
         self.device = device or torch.device("cpu")
         self.symm = symm
-        s = spec
-        assert s.num_heads % self.tp == 0, "num_heads must be divisible by tp_size"
-        self.hq, self.hkv = sharding.get_local_heads(self.rank, self.tp, s.num_heads, s.num_kv_heads)
-        self.kv_replicated = s.num_kv_heads < self.tp
-        self.vocab_padded = -(-s.vocab_size // self.tp) * self.tp
-        self._build_modules()
-        self.layers = [(layer_container_cls or layer_container_class(s))(self) for _ in range(s.num_layers)]
-        self.non_transformer = (non_transformer_container_cls or NonTransformerContainer)(self)
-        if state_dict is not None:
-            self.load_canonical(state_dict)
 
     # ---- facts the parameter classes ask for
     @property
@@ -439,11 +443,12 @@ class RaggedTransformer:
         n = batch.current_sequences
         if not (self._graphs_on and n == batch.current_tokens and n > 0 and batch.input_ids().is_cuda):
             return self.forward(batch, state_manager)
-        entry = self._graphs.get(n)
+        key = (n, batch.n_logit_rows)  # a step that returns other rows than one per sequence is another launch sequence
+        entry = self._graphs.get(key)
         if entry is None:
-            seen = self._graph_warm.get(n, 0)
+            seen = self._graph_warm.get(key, 0)
             if seen < 2:  # lazily built state (tensor maps, split heuristics, module buffers) settles in eager mode first
-                self._graph_warm[n] = seen + 1
+                self._graph_warm[key] = seen + 1
                 return self.forward(batch, state_manager)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
@@ -458,7 +463,7 @@ class RaggedTransformer:
                 return self.forward(batch, state_manager)
             if self._graph_pool is None:
                 self._graph_pool = g.pool()
-            entry = self._graphs[n] = (g, out)
+            entry = self._graphs[key] = (g, out)
         g, out = entry
         g.replay()
         return out.clone()  # the graph's output buffer is rewritten by the next replay

@@ -1,4 +1,4 @@
-from .attention_configs import DSSelfAttentionConfig, MaskingType, PositionalEmbeddingType, RotateHalfConfig
+from .attention_configs import DSLatentAttentionConfig, DSSelfAttentionConfig, MaskingType, PositionalEmbeddingType, RotateHalfConfig
 from .embedding_config import DSEmbeddingsConfig
 from .linear_config import DSLinearConfig
 from .moe_config import DSMoEConfig

@@ -58,3 +58,27 @@ class DSSelfAttentionConfig(DSModuleConfig):
     def group_size(self) -> int:
         """query heads served by one key/value head"""
         return self.n_heads_q // self.n_heads_kv
+
+
+class DSLatentAttentionConfig(DSModuleConfig):
+    """Attention whose keys and values are up-projections of one cached low-rank latent per token (no positional rotation):
+    c_q = rms(W_dq h), q = W_uq c_q;  c = rms(W_dkv h) is cached;  k = W_uk c, v = W_uv c per head; causal softmax."""
+    n_heads: int
+    qk_dim: int  # query / key size per head
+    v_dim: int  # value size per head
+    kv_rank: int  # size of the cached latent
+    q_rank: int  # size of the query latent
+    scale: float  # softmax scale (given, not derived from qk_dim)
+    eps: float = 1e-6  # of the two latent norms
+    max_sequences: int
+    input_dtype: DtypeEnum = DtypeEnum.bf16
+    output_dtype: DtypeEnum = DtypeEnum.bf16
+
+    @model_validator(mode="after")
+    def _positive(self):
+        for k in ("n_heads", "qk_dim", "v_dim", "kv_rank", "q_rank"):
+            if getattr(self, k) <= 0:
+                raise ValueError(f"{k} must be positive")
+        if self.kv_rank > 512:
+            raise ValueError("the latent attention kernels hold a latent row of at most 512 values")
+        return self

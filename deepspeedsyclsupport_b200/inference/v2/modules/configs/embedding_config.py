@@ -12,3 +12,6 @@ class DSEmbeddingsConfig(DSModuleConfig):
     positional_offset: int = 0  # OPT stores position p at row p + 2
     use_token_type: bool = False
     output_normalization: Optional[NormTypeEnum] = None
+    # not None: a fixed sinusoidal position vector is added (entry 2i = sin(p base^(-2i/dim)), entry 2i+1 = cos of the same) and the
+    # result is the fp32 start of the residual stream
+    sinusoidal_base: Optional[float] = None

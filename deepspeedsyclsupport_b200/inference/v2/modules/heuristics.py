@@ -2,9 +2,9 @@
 inference/v2/modules/heuristics.py:36-179).  Decisions here depend on the engine configuration, not on the model: the
 quantisation mode selects the fp8 tensor-core linear; everything else currently has one B200 implementation."""
 from ..config_v2 import RaggedInferenceEngineConfig
-from ..inference_utils import NormTypeEnum
+from ..inference_utils import ActivationType, NormTypeEnum
 from . import implementations  # noqa: F401  (registers the implementations)
-from .configs import DSEmbeddingsConfig, DSLinearConfig, DSMoEConfig, DSNormConfig, DSSelfAttentionConfig, DSUnembedConfig
+from .configs import DSLatentAttentionConfig, DSEmbeddingsConfig, DSLinearConfig, DSMoEConfig, DSNormConfig, DSSelfAttentionConfig, DSUnembedConfig
 from .interfaces import (DSEmbeddingBase, DSEmbeddingRegistry, DSLinearBase, DSLinearRegistry, DSMoEBase, DSMoERegistry, DSPostNormBase,
                          DSPostNormRegistry, DSPreNormBase, DSPreNormRegistry, DSSelfAttentionBase, DSSelfAttentionRegistry, DSUnembedBase,
                          DSUnembedRegistry)
@@ -16,12 +16,15 @@ def _quant_mode(engine_config) -> str:
     return getattr(q, "quantization_mode", "") or ""
 
 
-def instantiate_attention(attention_config: DSSelfAttentionConfig, engine_config: RaggedInferenceEngineConfig = None) -> DSSelfAttentionBase:
+def instantiate_attention(attention_config, engine_config: RaggedInferenceEngineConfig = None) -> DSSelfAttentionBase:
+    if isinstance(attention_config, DSLatentAttentionConfig):  # keys / values are up-projections of a cached latent
+        return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name="latent_blocked_attention", config=attention_config))
     return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name="dense_blocked_attention", config=attention_config))
 
 
 def instantiate_embed(embed_config: DSEmbeddingsConfig, engine_config: RaggedInferenceEngineConfig = None) -> DSEmbeddingBase:
-    return DSEmbeddingRegistry.instantiate_config(ConfigBundle(name="ragged_embedding", config=embed_config))
+    name = "sinusoidal_embedding" if embed_config.sinusoidal_base is not None else "ragged_embedding"
+    return DSEmbeddingRegistry.instantiate_config(ConfigBundle(name=name, config=embed_config))
 
 
 def instantiate_linear(linear_config: DSLinearConfig, engine_config: RaggedInferenceEngineConfig = None) -> DSLinearBase:
@@ -37,6 +40,8 @@ def instantiate_linear(linear_config: DSLinearConfig, engine_config: RaggedInfer
 
 
 def instantiate_moe(moe_config: DSMoEConfig, engine_config: RaggedInferenceEngineConfig = None) -> DSMoEBase:
+    if moe_config.n_groups > 1 or moe_config.use_correction or ActivationType(moe_config.activation) == ActivationType.ClampedSwiGLU:
+        return DSMoERegistry.instantiate_config(ConfigBundle(name="grouped_topk_moe", config=moe_config))
     bundle = ConfigBundle(name="cutlass_multi_gemm_moe", config=moe_config, implementation_config={"weight_dtype": moe_config.input_dtype})
     return DSMoERegistry.instantiate_config(bundle)
 
@@ -47,7 +52,7 @@ def instantiate_post_norm(norm_config: DSNormConfig, engine_config: RaggedInfere
 
 def instantiate_pre_norm(norm_config: DSNormConfig, engine_config: RaggedInferenceEngineConfig = None) -> DSPreNormBase:
     kind = NormTypeEnum(norm_config.type)
-    name = "cuda_pre_ln" if kind == NormTypeEnum.LayerNorm else "cuda_pre_rms"
+    name = "cuda_pre_ln" if kind == NormTypeEnum.LayerNorm else ("cuda_sandwich_rms" if norm_config.sandwich else "cuda_pre_rms")
     return DSPreNormRegistry.instantiate_config(ConfigBundle(name=name, config=norm_config))
 
 

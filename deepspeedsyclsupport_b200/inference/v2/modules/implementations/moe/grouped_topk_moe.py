@@ -1,0 +1,75 @@
+"""Mixture-of-experts MLP with a grouped, bias-corrected top-k router and a clamped gated activation.
+
+Router (fp32): scores = softmax(W_r h) over all experts; the CHOICE uses scores + correction, restricted to the `keep_groups`
+groups of neighbouring experts whose best choice score is largest; the combine WEIGHTS are the plain scores of the chosen
+experts (optionally renormalised).  Experts: two grouped GEMMs over the rows sorted by expert with the gated activation
+between them; the weighted combine leaves in fp32 (it feeds an fp32 norm / residual).
+
+The grouped GEMMs run on the persistent tcgen05 kernel (csrc/gemm/gemm_grouped.cu) when the operands are bf16 with
+TMA-compatible shapes, else on the CUDA-core grouped GEMM of csrc/ragged/latent_ops.cu (any shape, bf16 or true fp32)."""
+from typing import Any, Dict, Optional
+
+import torch
+
+from ......ops.gemm import dense_matmul, moe_gemm
+from .... import kernels as K
+from ....inference_parameter import InferenceParameter
+from ....inference_utils import ActivationType, DtypeEnum
+from ...configs import DSMoEConfig
+from ...interfaces import DSMoEBase, DSMoERegistry
+
+
+@DSMoERegistry.register_module
+class DSGroupedTopKMoE(DSMoEBase):
+
+    @staticmethod
+    def name() -> str:
+        return "grouped_topk_moe"
+
+    @staticmethod
+    def supports_config(config: DSMoEConfig) -> bool:
+        if config.input_dtype != config.output_dtype or DtypeEnum(config.input_dtype) not in (DtypeEnum.bf16, DtypeEnum.fp32):
+            return False
+        if ActivationType(config.activation) != ActivationType.ClampedSwiGLU:
+            return False
+        g, k = config.n_groups, config.keep_groups
+        return (1 <= config.top_k <= min(config.n_experts, 32) and config.n_experts <= 2048 and g >= 1 and config.n_experts % g == 0 and
+                1 <= k <= g and k * (config.n_experts // g) >= config.top_k)
+
+    def __init__(self, config: DSMoEConfig, implementation_config: Dict[str, Any] = None) -> None:
+        super().__init__(config, implementation_config)
+        self._dtype = DtypeEnum(config.input_dtype).value
+        self._output = None
+
+    def transform_gate_param(self, param: torch.Tensor) -> InferenceParameter:
+        return InferenceParameter.initialize(param.to(torch.float32).contiguous())  # router weights and correction: fp32
+
+    def transform_moe_mlp_1_param(self, param: torch.Tensor) -> InferenceParameter:
+        return InferenceParameter.initialize(param.to(self._dtype).contiguous())
+
+    def transform_moe_mlp_2_param(self, param: torch.Tensor) -> InferenceParameter:
+        return InferenceParameter.initialize(param.to(self._dtype).contiguous())
+
+    @property
+    def output(self) -> torch.Tensor:
+        return self._output
+
+    def _grouped(self, x, w, cumsum):
+        if x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and w.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0:
+            return moe_gemm(x, w, cumsum)
+        return K.moe_gemm_rows(x, w, cumsum)
+
+    def forward(self, hidden_states: torch.Tensor, gate_w: torch.Tensor, mlp_1_w: torch.Tensor, mlp_2_w: torch.Tensor,
+                mlp_1_b: Optional[torch.Tensor] = None, mlp_2_b: Optional[torch.Tensor] = None,
+                correction: Optional[torch.Tensor] = None) -> torch.Tensor:
+        c = self._config
+        assert mlp_1_b is None and mlp_2_b is None, "these experts have no biases"
+        assert (correction is not None) == c.use_correction
+        logits = dense_matmul(hidden_states.float(), gate_w)  # fp32 router logits from the (already rounded) activations
+        counts, scores, assignments, offsets = K.grouped_topk_gating(logits, c.top_k, correction, c.n_groups, c.keep_groups, c.normalize_scores)
+        moe_in, cumsum, slots = K.moe_scatter_rows(hidden_states, counts, assignments, offsets)
+        gu = self._grouped(moe_in, mlp_1_w, cumsum)
+        act = K.clamped_swish_gate(gu, c.act_alpha, c.act_limit, c.act_shift)
+        out = self._grouped(act, mlp_2_w, cumsum)
+        self._output = K.moe_gather_rows(out, scores, slots)
+        return self._output

@@ -1,2 +1,3 @@
 from .cuda_pre_ln import DSPreLNCUDAModule
 from .cuda_pre_rms import DSPreRMSCUDAModule
+from .cuda_sandwich_rms import DSSandwichRMSNorm

@@ -4,7 +4,7 @@ from typing import Any, Dict, Optional
 import torch
 
 from ......ops import fused_ops as FO
-from ......ops.gemm import gemm
+from ......ops.gemm import dense_matmul, gemm
 from .... import kernels as K
 from ....inference_utils import DtypeEnum, NormTypeEnum
 from ...configs import DSUnembedConfig
@@ -36,7 +36,10 @@ class DSRaggedUnembed(DSUnembedBase):
                 residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         """`residual` (optional): the residual stream the last hidden state still has to be added to -- only the gathered rows
         (one per sequence) are added and normalised, not the whole batch."""
-        last_tok = ragged_metadata.last_tokens()
+        last_tok = ragged_metadata.logit_rows()
+        c = self._config
+        if c.residual_fp32:
+            return self._forward_fp32_residual(hidden_states, vocab_embedding, last_tok, gamma)
         h = K.logits_gather(hidden_states, last_tok)
         r = K.logits_gather(residual, last_tok) if residual is not None else None
         if self._norm == NormTypeEnum.RMSNorm:
@@ -53,5 +56,24 @@ class DSRaggedUnembed(DSUnembedBase):
             logits = torch.nn.functional.linear(h, vocab_embedding)
         if bias is not None:
             logits = logits + bias
+        if c.logit_softcap > 0:
+            logits = c.logit_softcap * torch.tanh(logits.float() / c.logit_softcap)
+        self._output = logits
+        return logits
+
+    def _forward_fp32_residual(self, residual, vocab_embedding, rows, gamma):
+        """Gather + RMS norm of the wanted rows in one kernel (fp32 in, activation dtype out), projection with fp32 logits,
+        soft cap in place."""
+        c = self._config
+        assert self._norm == NormTypeEnum.RMSNorm and residual.dtype == torch.float32
+        act = DtypeEnum(c.dtype).value
+        if rows.numel() == 0:
+            return torch.empty(0, vocab_embedding.shape[0], dtype=torch.float32, device=residual.device)
+        h = K.sandwich_norm(residual, w=gamma, o=c.norm_weight_offset, eps=c.eps, out_dtype=act, rows=rows)
+        logits = dense_matmul(h, vocab_embedding, out_dtype=torch.float32)
+        if not logits.is_contiguous():
+            logits = logits.contiguous()
+        if c.logit_softcap > 0:
+            K.softcap_(logits, c.logit_softcap)
         self._output = logits
         return logits

@@ -14,8 +14,10 @@ class BlockedKVCache:
     def __init__(self, config: KVCacheConfig, memory_config: MemoryConfig, mp_group=None, offload=False):
         self._config = config
         num_layers, num_heads, head_size = config.cache_shape
-        dtype = {"bf16": torch.bfloat16, "fp16": torch.float16}[config.cache_dtype]
-        per_block = 2 * config.block_size * num_heads * head_size * num_layers * torch.empty(0, dtype=dtype).element_size()
+        dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[config.cache_dtype]
+        shapes = config.layer_shapes
+        per_token = 2 * num_heads * head_size * num_layers if shapes is None else sum(p * h * d for p, h, d in shapes)
+        per_block = config.block_size * per_token * torch.empty(0, dtype=dtype).element_size()
         if memory_config.mode in (AllocationMode.RESERVE, AllocationMode.RESERVE.value):
             acc = get_accelerator()
             if acc.device_name() == "cuda":
@@ -34,7 +36,11 @@ class BlockedKVCache:
         self._num_blocks = num_blocks
         device = get_accelerator().current_device_name()
         logger.info(f"Allocating KV-cache with {num_blocks} blocks ({per_block * num_blocks / 2 ** 30:.2f} GiB)")
-        self._cache = torch.zeros(num_layers, num_blocks, 2, config.block_size, num_heads, head_size, dtype=dtype, device=device)
+        if shapes is None:
+            self._cache = torch.zeros(num_layers, num_blocks, 2, config.block_size, num_heads, head_size, dtype=dtype, device=device)
+        else:  # one tensor per cached layer; a single plane is dropped from the shape: [blocks, block_size, heads, head_size]
+            self._cache = [torch.zeros((num_blocks, ) + ((p, ) if p != 1 else ()) + (config.block_size, h, d), dtype=dtype, device=device)
+                           for p, h, d in shapes]
         self._allocator = BlockedAllocator(num_blocks)
 
     def reserve(self, num_blocks: int) -> torch.Tensor:
@@ -66,6 +72,7 @@ class BlockedKVCache:
     def offload(self, blocks) -> torch.Tensor:
         """Copy the given blocks of every layer to pinned host memory and return the host tensor
         [layers, n, 2, block, heads, head_size]; the blocks themselves stay allocated (reference: kv_cache.offload)."""
+        assert torch.is_tensor(self._cache), "offload is implemented for uniform caches"
         idx = torch.as_tensor(blocks, dtype=torch.long, device=self._cache.device)
         picked = self._cache.index_select(1, idx)
         host = torch.empty(picked.shape, dtype=picked.dtype, device="cpu",

@@ -1,6 +1,6 @@
 """State-manager / KV-cache configuration (parity: inference/v2/ragged/manager_configs.py:137-183)."""
 from enum import Enum
-from typing import Optional, Tuple
+from typing import List, Optional, Tuple
 
 from pydantic import Field, model_validator
 
@@ -21,7 +21,11 @@ class KVCacheConfig(DeepSpeedConfigModel):
     block_size: int = 128
     num_allocation_groups: int = 1
     cache_shape: Tuple[int, int, int]  # (num_layers, num_kv_heads, head_size)
-    cache_dtype: str = "bf16"
+    cache_dtype: str = "bf16"  # bf16 | fp16 | fp32
+    # Caches whose layers differ, or that hold something other than a key and a value plane per token: one
+    # (planes, heads, head_size) per cached layer -- e.g. (1, 1, rank) for a layer that caches one latent row per token.
+    # When given, `cache_shape` only documents the number of layers; every layer shares the block ids.
+    layer_shapes: Optional[List[Tuple[int, int, int]]] = None
     max_blocks_per_allocation_group: int = 64
 
 

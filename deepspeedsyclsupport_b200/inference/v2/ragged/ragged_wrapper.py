@@ -39,13 +39,16 @@ class RaggedBatchWrapper:
         self._h_tok_seq = host(self.max_tokens, torch.int32)
         self._h_tok_pos = host(self.max_tokens, torch.int32)
         self._h_last = host(self.max_seqs, torch.int32)
+        self._h_rows = host(self.max_tokens, torch.int32)
         self.max_blocks_per_seq = -(-config.max_context // 1)  # set by the state manager
         self._d_ids = torch.zeros(self.max_tokens, dtype=torch.int64, device=dev)
         self._d_tok_seq = torch.zeros(self.max_tokens, dtype=torch.int32, device=dev)
         self._d_tok_pos = torch.zeros(self.max_tokens, dtype=torch.int32, device=dev)
         self._d_last = torch.zeros(self.max_seqs, dtype=torch.int32, device=dev)
+        self._d_rows = torch.zeros(self.max_tokens, dtype=torch.int32, device=dev)
         self._h_block_table = None
         self._d_block_table = None
+        self._copied = None  # CUDA event behind the last batch's host -> device copies
         self.clear()
 
     def set_block_table_shape(self, max_blocks_per_seq):
@@ -56,9 +59,29 @@ class RaggedBatchWrapper:
         self._d_block_table = torch.zeros_like(t, device=get_accelerator().current_device_name())
 
     def clear(self):
+        # The pinned shadows are about to be rewritten: the previous batch's asynchronous copies out of them must have run.  (A
+        # caller that reads every step's logits has waited already; one that skips the read, or a step replayed from a CUDA graph
+        # behind a long queue, has not.)
+        if self._copied is not None:
+            self._copied.synchronize()
+            self._copied = None
         self._n_tokens = 0
         self._n_seqs = 0
         self._seq_ntok, self._seq_seen, self._seq_start = [], [], []
+        self._n_rows = None  # None: logits of the last token of every sequence
+
+    def set_logit_positions(self, positions):
+        """positions[i]: indices into sequence i's tokens OF THIS BATCH whose logits the caller wants (may be empty).  Call after
+        the sequences are inserted and before `finalize`.  Without it the batch asks for the last token of every sequence."""
+        assert len(positions) == self._n_seqs
+        n = 0
+        for start, ntok, want in zip(self._seq_start, self._seq_ntok, positions):
+            for p in want:
+                if not 0 <= int(p) < ntok:
+                    raise ValueError(f"logit position {p} outside the {ntok} tokens of this step")
+                self._h_rows[n] = start + int(p)
+                n += 1
+        self._n_rows = n
 
     def insert_sequence(self, seq_descriptor, tokens, do_checks=True):
         n = tokens.numel()
@@ -86,7 +109,12 @@ class RaggedBatchWrapper:
         self._d_tok_seq[:self._n_tokens].copy_(self._h_tok_seq[:self._n_tokens], non_blocking=True)
         self._d_tok_pos[:self._n_tokens].copy_(self._h_tok_pos[:self._n_tokens], non_blocking=True)
         self._d_last[:self._n_seqs].copy_(self._h_last[:self._n_seqs], non_blocking=True)
+        if self._n_rows:
+            self._d_rows[:self._n_rows].copy_(self._h_rows[:self._n_rows], non_blocking=True)
         self._d_block_table[:self._n_seqs].copy_(self._h_block_table[:self._n_seqs], non_blocking=True)
+        if self._d_ids.is_cuda:
+            self._copied = torch.cuda.Event()
+            self._copied.record()
 
     # device views
     def input_ids(self):
@@ -100,6 +128,14 @@ class RaggedBatchWrapper:
 
     def last_tokens(self):
         return self._d_last[:self._n_seqs]
+
+    def logit_rows(self):
+        """Batch rows whose logits the step returns: the wanted positions when they were set, else every sequence's last token."""
+        return self._d_last[:self._n_seqs] if self._n_rows is None else self._d_rows[:self._n_rows]
+
+    @property
+    def n_logit_rows(self):
+        return self._n_seqs if self._n_rows is None else self._n_rows
 
     def block_table(self):
         return self._d_block_table

@@ -82,6 +82,33 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=torch.bfloat16, ac
     return out
 
 
+def tma_gemm_ok(x, w, out_dtype=torch.bfloat16):
+    """Whether `gemm(x, w)` can take these operands: bf16, unit inner strides, and row strides / base addresses that are
+    multiples of 16 bytes (every operand travels by TMA)."""
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2 and x.shape[0] > 0 and
+            x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and
+            w.data_ptr() % 16 == 0 and x.shape[1] % 8 == 0)
+
+
+def dense_matmul(x, w, out_dtype=None):
+    """x [M, K] @ w[N, K]^T for any shape and for bf16 or fp32 operands.  bf16 operands with TMA-compatible strides run on the
+    tcgen05 kernels (fp32 accumulation; `out_dtype` bf16 or fp32); everything else goes to the vendor GEMM: bf16 with odd
+    strides, and fp32 in true fp32 -- the reduced-precision TF32 mode is switched off around the call."""
+    out_dtype = out_dtype or x.dtype
+    if tma_gemm_ok(x, w, out_dtype):
+        return gemm(x, w, out_dtype=out_dtype)
+    if x.dtype == torch.float32 and x.is_cuda:
+        keep = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        try:
+            y = torch.nn.functional.linear(x, w)
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = keep
+        return y if out_dtype == y.dtype else y.to(out_dtype)
+    y = torch.nn.functional.linear(x, w)
+    return y if out_dtype == y.dtype else y.to(out_dtype)
+
+
 FP8_MAX = 448.0  # largest finite e4m3 value
 _ROWQ_DT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 native.register_sigs({"dsb200_fp8_rowwise_quantize": "ppp ii l i p", "dsb200_gemm_fp8_block": "ppppp iii iii i p",

@@ -22,8 +22,39 @@ class NativeError(RuntimeError):
     pass
 
 
+_components = None  # sub-folders of csrc/ this process needs from the device library; None = all of them
+
+
+def require_components(components):
+    """Call before the first `lib()`: when the device library has to be (re)built for this process, only these sub-folders of
+    csrc/ are compiled (plus whatever an earlier build already holds).  A process that never calls this gets the whole library."""
+    global _components
+    _components = sorted(set(components))
+
+
+def _ensure_device_components():
+    """Build or extend libdsb200.so so that it holds what this process asked for."""
+    from .op_builder import builder
+    have = builder.built_components()
+    exists = os.path.exists(os.path.join(_LIB_DIR, "libdsb200.so"))
+    if _components is None:
+        if exists and have is None:
+            return
+        builder.build_device()
+    else:
+        if exists and (have is None or set(_components) <= have):
+            return
+        builder.build_device(components=sorted(set(_components) | (have or set())))
+
+
 def _load(name, build_fn):
     path = os.path.join(_LIB_DIR, name)
+    if name == "libdsb200.so":
+        try:
+            _ensure_device_components()
+        except Exception as e:  # pragma: no cover
+            if not os.path.exists(path):
+                raise NativeError(f"{name} is not built and building it failed: {e}")
     if not os.path.exists(path):
         try:
             from .op_builder import builder

@@ -44,8 +44,29 @@ def _digest(paths, extra=""):
     return h.hexdigest()
 
 
-def device_sources():
-    return sorted(glob.glob(os.path.join(CSRC, "**", "*.cu"), recursive=True))
+def device_sources(components=None):
+    """Every csrc/**/*.cu, or only the files named by `components`: paths relative to csrc/, a folder standing for all of its files
+    ("ragged", "gemm/gemm_bf16.cu"); csrc/common is always included."""
+    srcs = sorted(glob.glob(os.path.join(CSRC, "**", "*.cu"), recursive=True))
+    if components is None:
+        return srcs
+    keep = set(c.strip("/") for c in components) | {"common"}
+
+    def wanted(src):
+        rel = os.path.relpath(src, CSRC).replace(os.sep, "/")
+        return any(rel == k or rel.startswith(k + "/") for k in keep)
+
+    return [s for s in srcs if wanted(s)]
+
+
+def _flags_for(src):
+    """A source whose first lines carry `// build: precise-math` is compiled without --use_fast_math: IEEE division and square
+    root, accurate expf / tanhf / sincos and no flush-to-zero (kernels whose results are compared in true fp32)."""
+    with open(src) as f:
+        head = f.read(400)
+    if "// build: precise-math" in head:
+        return [f for f in NVCC_FLAGS if f != "--use_fast_math"]
+    return NVCC_FLAGS
 
 
 def host_sources():
@@ -65,8 +86,19 @@ def _run(cmd):
     return r.stdout
 
 
-def build_device(force=False, verbose=False):
-    """Compile every csrc/**/*.cu into lib/libdsb200.so (incremental per translation unit)."""
+def built_components():
+    """Sub-folders of csrc/ the existing libdsb200.so was linked from (None: no library, or one linked from everything)."""
+    stamp = os.path.join(LIB_DIR, "libdsb200.so.components")
+    if not os.path.exists(os.path.join(LIB_DIR, "libdsb200.so")) or not os.path.exists(stamp):
+        return None
+    txt = open(stamp).read().strip()
+    return None if txt == "*" else set(txt.split())
+
+
+def build_device(force=False, verbose=False, components=None):
+    """Compile csrc/**/*.cu into lib/libdsb200.so (incremental per translation unit).  `components`: only these sub-folders
+    of csrc/ (a serving process that needs the inference kernels does not wait for the training ones); entry points of the
+    others are then absent from the library until a later call without `components` adds them."""
     nvcc = nvcc_path()
     if nvcc is None:
         raise RuntimeError("nvcc not found")
@@ -75,7 +107,7 @@ def build_device(force=False, verbose=False):
     out = os.path.join(LIB_DIR, "libdsb200.so")
     hdr_digest = _digest(_headers(), " ".join(NVCC_FLAGS))
     objs, jobs = [], []
-    for src in device_sources():
+    for src in device_sources(components):
         rel = os.path.relpath(src, CSRC).replace(os.sep, "__")
         obj = os.path.join(BUILD_DIR, rel + ".o")
         stamp = obj + ".sha1"
@@ -87,7 +119,7 @@ def build_device(force=False, verbose=False):
 
     def compile_one(job):
         src, obj, stamp, want = job
-        log = _run([nvcc] + NVCC_FLAGS + ["-I", os.path.join(REPO_ROOT, "include"), "-c", src, "-o", obj])
+        log = _run([nvcc] + _flags_for(src) + ["-I", os.path.join(REPO_ROOT, "include"), "-c", src, "-o", obj])
         with open(stamp, "w") as f:
             f.write(want)
         if verbose and log.strip():
@@ -96,8 +128,15 @@ def build_device(force=False, verbose=False):
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(compile_one, jobs))
-    if jobs or not os.path.exists(out):
-        _run([nvcc, "-shared", "-o", out] + objs + ["-lcudart"])
+    comp_stamp = out + ".components"
+    comp_txt = "*" if components is None else " ".join(sorted(set(components) | {"common"}))
+    have_comp = open(comp_stamp).read().strip() if os.path.exists(comp_stamp) else None
+    if jobs or not os.path.exists(out) or have_comp != comp_txt:
+        tmp = out + ".tmp%d" % os.getpid()  # link beside the target and rename: a concurrent loader never sees half a file
+        _run([nvcc, "-shared", "-o", tmp] + objs + ["-lcudart"])
+        os.replace(tmp, out)
+        with open(comp_stamp, "w") as f:
+            f.write(comp_txt)
     return out
 
 

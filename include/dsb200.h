@@ -356,6 +356,58 @@ int dsb200_fake_quantize(void* x, long long groups, int group_size, int bits, in
 int dsb200_fp8_rowwise_quantize(const void* x, void* q, float* scales, int rows, int cols, long long ldx, int dtype,
                                 dsb200_stream_t stream);
 
+/* ---- csrc/ragged/latent_ops.cu */
+/* out[t, :] = table[ids[t], :] + sinusoid(tok_pos[t]): entry 2i = sin(p f_i), entry 2i + 1 = cos(p f_i); `freq` holds the
+ * ceil(dim / 2) frequencies as doubles on the device.  table_dtype: 0 = bf16, 1 = fp32.  out is fp32. */
+int dsb200_embed_sinusoid(const long long* ids, const void* table, int table_dtype, const int* tok_pos, const double* freq,
+                          float* out, int n_tokens, int dim, dsb200_stream_t stream);
+/* Per row of the fp32 residual x [n_rows, dim] (row rows[r] when `rows` is given): if y: x += rms_norm(y) * (wb + ob); if w:
+ * out = rms_norm(x) * (w + o).  y and out are bf16 (dtype 0) or fp32 (dtype 1); the weights are fp32. */
+int dsb200_sandwich_norm(float* x, const void* y, int y_dtype, const float* wb, float ob, const float* w, float o,
+                         void* out, int out_dtype, const int* rows, int n_rows, int dim, float eps,
+                         dsb200_stream_t stream);
+/* lat [n_tokens, ld] holds (query latent [nq] | key/value latent [nkv]) of every token.  cq [n_tokens, nq] = plain-weight RMS norm
+ * of the first part; the RMS-normed second part is written to the token's row of cache [blocks, block_size, nkv]. */
+int dsb200_latent_norm_append(const void* lat, int ld, const float* wq, const float* wkv, void* cq, void* cache,
+                              const int* tok_seq, const int* tok_pos, const int* block_table, int bt_stride,
+                              int block_size, int n_tokens, int nq, int nkv, float eps, int dtype, dsb200_stream_t stream);
+/* floats of scratch `dsb200_latent_attention` needs for n_splits > 1 */
+long long dsb200_latent_attention_scratch_floats(int n_tokens, int H, int R, int n_splits);
+/* out[t, h, :] = sum_j softmax_j(scale * q[t, h, :] . c_j) c_j over the cached latents c_0 .. c_pos(t) of the token's sequence.
+ * q: bf16 / fp32 (q_dtype 0 / 1) with element strides per token and head; cache [blocks, block_size, R] bf16 / fp32 (cache_dtype);
+ * out fp32 with element strides per token and head.  R <= 512. */
+int dsb200_latent_attention(const void* q, int q_dtype, long long q_tok_stride, long long q_head_stride, const void* cache,
+                            int cache_dtype, float* out, long long o_tok_stride, long long o_head_stride, float* scratch,
+                            const int* tok_seq, const int* tok_pos, const int* block_table, int bt_stride, int block_size,
+                            int n_tokens, int H, int R, float scale, int n_splits, dsb200_stream_t stream);
+/* a[r, c] *= sigmoid(g[r, c]) over [rows, cols] with row strides (elements).  dtype 0 = bf16, 1 = fp32. */
+int dsb200_sigmoid_gate_mul(void* a, long long a_ld, const void* g, long long g_ld, long long rows, int cols, int dtype,
+                            dsb200_stream_t stream);
+/* gu [rows, 2 F] = (gate | up) -> out [rows, F] = g' * sigmoid(alpha g') * (clamp(u, -limit, limit) + shift), g' = min(g, limit) */
+int dsb200_clamped_swish_gate(const void* gu, void* out, long long rows, int F, float alpha, float limit, float shift,
+                              int dtype, dsb200_stream_t stream);
+/* x[r, c] = cap * tanh(x[r, c] / cap) over fp32 [rows, cols] with row stride ld */
+int dsb200_softcap(float* x, long long ld, long long rows, int cols, float cap, dsb200_stream_t stream);
+/* Router: softmax over the E logits of a token; choice score = score + correction[e] (correction may be null); experts are split
+ * into `groups` equal neighbour groups, of which the `keep` with the largest maximal choice score stay selectable; the top_k
+ * selectable experts by choice score are assigned; their weights are the uncorrected scores (divided by their sum when
+ * `normalize`).  Outputs as dsb200_top_k_gating; expert_counts must be zeroed by the caller. */
+int dsb200_grouped_topk_gating(const float* logits, const float* correction, int* expert_counts, float* scores,
+                               int* assignments, int* offsets, int n_tokens, int n_experts, int top_k, int groups,
+                               int keep, int normalize, dsb200_stream_t stream);
+/* Rows of x [n_tokens, dim] copied into expert-sorted order (any dim; dtype 0 = bf16, 1 = fp32); also writes the inclusive
+ * per-expert row cumsum and every (token, k)'s row. */
+int dsb200_moe_scatter_rows(const void* x, const int* expert_counts, const int* assignments, const int* offsets,
+                            long long* expert_cumsum, void* moe_in, int* mapped_slots, int n_tokens, int n_experts,
+                            int dim, int top_k, int dtype, dsb200_stream_t stream);
+/* out[t, :] (fp32) = sum_k scores[t, k] * moe_out[mapped_slots[t, k], :] */
+int dsb200_moe_gather_rows(const void* moe_out, const float* scores, const int* mapped_slots, float* out, int n_tokens,
+                           int dim, int top_k, int dtype, dsb200_stream_t stream);
+/* Grouped expert GEMM on CUDA cores: out[r, :] = w[expert(r)] x[r, :] for the R rows sorted by expert; x [R, K], w [E, N, K],
+ * out [R, N], all bf16 (dtype 0) or all fp32 (dtype 1), contiguous; fp32 accumulation.  expert_cumsum [E] int64 on the device. */
+int dsb200_moe_gemm_rows(const void* x, const void* w, void* out, const long long* expert_cumsum, int R, int N, int K,
+                         int E, int dtype, dsb200_stream_t stream);
+
 /* ---- csrc/ragged/ragged_ops.cu */
 int dsb200_kv_rotary_append(void* qkv, void* kv_cache, const int* tok_seq, const int* tok_pos, const int* block_table,
                             const float* inv_freq, int n_tokens, int hq, int hkv, int head_dim, int block_size,
