@@ -30,7 +30,7 @@ class InferenceEngineV2:
         self._model = model_builder(self._tp_group, self.device)
         spec = self._model.spec
         block = int(getattr(engine_config.state_manager, "kv_block_size", 0) or 0) or (128 if self.device.type == "cuda" else 16)
-        if hasattr(self._model, "kv_cache_config"):  # models whose cached layers differ from (key, value) x heads describe them
+        if getattr(self._model, "describes_own_cache", False):  # cached layers that are not (key, value) x heads: the model lays them out
             kv_cfg = self._model.kv_cache_config(block_size=block)
         else:
             kv_cfg = KVCacheConfig(block_size=block,

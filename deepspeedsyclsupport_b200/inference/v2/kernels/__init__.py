@@ -272,7 +272,8 @@ def sandwich_norm(x, y=None, wb=None, ob=0.0, w=None, o=0.0, eps=1e-6, out_dtype
     n = x.shape[0] if rows is None else rows.numel()
     out = torch.empty(n, x.shape[1], dtype=out_dtype, device=x.device) if w is not None else None
     if y is not None:
-        assert y.is_contiguous() and y.shape == x.shape
+        assert y.shape == x.shape
+        y = y if y.is_contiguous() else y.contiguous()  # a GEMM output whose rows were padded to the TMA stride (odd widths only)
     native.check(native.lib().dsb200_sandwich_norm(native.ptr(x), native.ptr(y), _dt(y) if y is not None else 0, native.ptr(wb), float(ob),
                                                    native.ptr(w), float(o), native.ptr(out), _DT[out_dtype], native.ptr(rows), n, x.shape[1],
                                                    float(eps), native.stream_ptr()))

@@ -106,6 +106,7 @@ class LinasunSpec:
 
 
 class LinasunInferenceModel(RaggedTransformer, DSInferenceModelBase):
+    describes_own_cache = True  # the engine builds its paged cache from `kv_cache_config` below
 
     def __init__(self, spec: LinasunSpec, tp_group=None, dtype=torch.bfloat16, device=None, engine_config=None, layer_container_cls=None,
                  non_transformer_container_cls=None, quantization_mode=""):

@@ -30,3 +30,6 @@ class LinasunPolicy(InferenceV2Policy):
         cmap.set_transformer_params("l", self.model.layers)
         cmap.set_non_transformer_params(self.model.non_transformer)
         return cmap
+
+    def finish_loading(self, cmap: ContainerMap) -> None:
+        self.model.check_populated()  # a layer with a feed-forward needs ALL of its feed-forward tensors

@@ -12,7 +12,7 @@ from typing import Any, Dict, Optional
 import torch
 
 from ......ops import fused_ops as FO
-from ......ops.gemm import gemm, linear_fp8, linear_fp8_block, linear_mxfp8, quantize_fp8_rowwise, quantize_mxfp8
+from ......ops.gemm import dense_matmul, gemm, linear_fp8, linear_fp8_block, linear_mxfp8, quantize_fp8_rowwise, quantize_mxfp8
 from ....inference_parameter import InferenceParameter
 from ....inference_utils import ActivationType, DtypeEnum, activation_name, is_gated
 from ...configs import DSLinearConfig
@@ -68,8 +68,8 @@ class BlasFPLinear(_LinearCommon):
         return InferenceParameter.initialize(param.to(DtypeEnum(self._config.input_dtype).value).contiguous())
 
     def forward(self, hidden_states: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -> torch.Tensor:
-        if hidden_states.is_cuda and hidden_states.dtype == torch.bfloat16:
-            y = gemm(hidden_states, w)
+        if hidden_states.is_cuda:
+            y = dense_matmul(hidden_states, w)  # tcgen05 kernels for bf16 with TMA-compatible strides, vendor GEMM otherwise (fp32: no TF32)
         else:
             y = torch.nn.functional.linear(hidden_states, w)
         return self._epilogue(y, b)
