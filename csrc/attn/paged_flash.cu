@@ -61,6 +61,7 @@ struct Params {
   float* part_o;           // [T][hq][n_splits][D]   (n_splits > 1)
   float* part_ml;          // [T][hq][n_splits][2]
   int T, hq, hkv, group, nt_tile, block_size, max_blocks, n_splits;
+  int kv_planes;  // 2: a block holds a key plane and a value plane; 1: one plane serves as both (latent caches: keys == values)
   float scale_log2;
   int window;          // local attention: keys [pos - window + 1, pos] are visible; 0 = the whole history
   const float* alibi;  // optional [hq] ALiBi slopes: score += slope[head] * key position (BLOOM / MPT / falcon-rw); nullptr = none
@@ -194,7 +195,7 @@ paged_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
               const int blk = bt[logical];
               const int row_off = s * p.block_size * 128;
 #pragma unroll
-              for (int c = 0; c < NCH; ++c) tma_load_4d(&tmKV, full, tile + c * CHUNK_BYTES + row_off, c * 64, kvh, 0, blk * 2 + is_v);
+              for (int c = 0; c < NCH; ++c) tma_load_4d(&tmKV, full, tile + c * CHUNK_BYTES + row_off, c * 64, kvh, 0, blk * p.kv_planes + (is_v & (p.kv_planes - 1)));
             }
           }
           if (++st == NS) { st = 0; ph ^= 1; }
@@ -582,7 +583,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
               const int blk = bt[logical];
               const int row_off = s * p.block_size * 128;
 #pragma unroll
-              for (int c = 0; c < 2; ++c) tma_load_4d(&tmKV, full, tile + c * CHUNK_BYTES + row_off, c * 64, kvh, 0, blk * 2 + is_v);
+              for (int c = 0; c < 2; ++c) tma_load_4d(&tmKV, full, tile + c * CHUNK_BYTES + row_off, c * 64, kvh, 0, blk * p.kv_planes + (is_v & (p.kv_planes - 1)));
             }
           }
           if (++st == NS) { st = 0; ph ^= 1; }
@@ -829,10 +830,10 @@ __global__ void combine_splits_kernel(const float* __restrict__ part_o, const fl
 template <int D>
 static int launch(const void* qkv, const void* kv_cache, void* out, const int* tok_seq, const int* tok_pos, const int* block_table,
                   int T, int hq, int hkv, int block_size, int max_blocks, int num_blocks, float scale, int max_atoms, int n_splits,
-                  void* scratch, const float* alibi, int window, cudaStream_t stream) {
+                  void* scratch, const float* alibi, int window, cudaStream_t stream, int q_row_heads = 0, int kv_planes = 2) {
   using SMEM = Smem<D>;
   const int group = hq / hkv, nt_tile = BM / group;
-  const int heads = hq + 2 * hkv;
+  const int heads = q_row_heads ? q_row_heads : hq + 2 * hkv;  // heads per row of the query tensor
   CUtensorMap tmQ, tmKV;
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(heads), static_cast<uint64_t>(T)};
@@ -843,7 +844,7 @@ static int launch(const void* qkv, const void* kv_cache, void* out, const int* t
   }
   {
     const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(hkv), static_cast<uint64_t>(block_size),
-                              static_cast<uint64_t>(num_blocks) * 2};
+                              static_cast<uint64_t>(num_blocks) * kv_planes};
     const uint64_t strides[3] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(hkv) * D * 2,
                                  static_cast<uint64_t>(block_size) * hkv * D * 2};
     const uint32_t box[4] = {64, 1, static_cast<uint32_t>(block_size), 1};
@@ -868,7 +869,7 @@ static int launch(const void* qkv, const void* kv_cache, void* out, const int* t
   p.tok_seq = tok_seq; p.tok_pos = tok_pos; p.block_table = block_table; p.atoms = atoms; p.n_atoms = n_atoms;
   p.out = static_cast<__nv_bfloat16*>(out); p.part_o = part_o; p.part_ml = part_ml;
   p.T = T; p.hq = hq; p.hkv = hkv; p.group = group; p.nt_tile = nt_tile; p.block_size = block_size; p.max_blocks = max_blocks;
-  p.n_splits = n_splits; p.scale_log2 = scale * 1.4426950408889634f; p.alibi = alibi; p.window = window;
+  p.n_splits = n_splits; p.kv_planes = kv_planes; p.scale_log2 = scale * 1.4426950408889634f; p.alibi = alibi; p.window = window;
   static const bool want_trace = [] { const char* e = getenv("DSB200_PF_TRACE"); return e && atoi(e) != 0; }();
   static long long* trace_buf = nullptr;
   p.trace = nullptr;
@@ -901,10 +902,11 @@ static int launch(const void* qkv, const void* kv_cache, void* out, const int* t
 // decode variant: atoms of at most 16 / group tokens, head_dim 128
 static int launch_decode(const void* qkv, const void* kv_cache, void* out, const int* tok_seq, const int* tok_pos, const int* block_table,
                          int T, int hq, int hkv, int block_size, int max_blocks, int num_blocks, float scale, int max_atoms,
-                         int n_splits, void* scratch, const float* alibi, int window, cudaStream_t stream) {
+                         int n_splits, void* scratch, const float* alibi, int window, cudaStream_t stream, int q_row_heads = 0,
+                         int kv_planes = 2) {
   constexpr int D = 128;
   const int group = hq / hkv, nt_tile = NQ / group;
-  const int heads = hq + 2 * hkv;
+  const int heads = q_row_heads ? q_row_heads : hq + 2 * hkv;
   CUtensorMap tmQ, tmKV;
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(heads), static_cast<uint64_t>(T)};
@@ -915,7 +917,7 @@ static int launch_decode(const void* qkv, const void* kv_cache, void* out, const
   }
   {
     const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(hkv), static_cast<uint64_t>(block_size),
-                              static_cast<uint64_t>(num_blocks) * 2};
+                              static_cast<uint64_t>(num_blocks) * kv_planes};
     const uint64_t strides[3] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(hkv) * D * 2,
                                  static_cast<uint64_t>(block_size) * hkv * D * 2};
     const uint32_t box[4] = {64, 1, static_cast<uint32_t>(block_size), 1};
@@ -935,7 +937,7 @@ static int launch_decode(const void* qkv, const void* kv_cache, void* out, const
   p.tok_seq = tok_seq; p.tok_pos = tok_pos; p.block_table = block_table; p.atoms = nullptr; p.n_atoms = nullptr;
   p.out = static_cast<__nv_bfloat16*>(out); p.part_o = part_o; p.part_ml = part_ml;
   p.T = T; p.hq = hq; p.hkv = hkv; p.group = group; p.nt_tile = nt_tile; p.block_size = block_size; p.max_blocks = max_blocks;
-  p.n_splits = n_splits; p.scale_log2 = scale * 1.4426950408889634f; p.trace = nullptr; p.alibi = alibi; p.window = window;
+  p.n_splits = n_splits; p.kv_planes = kv_planes; p.scale_log2 = scale * 1.4426950408889634f; p.trace = nullptr; p.alibi = alibi; p.window = window;
   static const bool want_trace = [] { const char* e = getenv("DSB200_PF_TRACE"); return e && atoi(e) != 0; }();
   static long long* trace_buf = nullptr;
   if (want_trace) {
@@ -1012,4 +1014,30 @@ DSB_EXPORT int dsb200_paged_flash_decode(const void* qkv, const void* kv_cache, 
   DSB_REQUIRE(max_atoms >= 1 && n_splits >= 1 && n_splits <= 64 && scratch != nullptr, "paged_flash_decode: bad max_atoms / n_splits / scratch");
   return paged::launch_decode(qkv, kv_cache, out, tok_seq, tok_pos, block_table, n_tokens, hq, hkv, block_size, max_blocks_per_seq,
                               num_blocks, scale, max_atoms, n_splits, scratch, alibi_slopes, window, stream);
+}
+
+// Attention over a paged cache of latents: every one of the `heads` query heads of a token attends to the SAME cached rows, which
+// serve as keys and as values (one plane per block: cache [num_blocks][block_size][rank], bf16).  q and out are [n_tokens][heads][rank]
+// bf16; rank 64 or 128; heads must divide 128 (callers pad with zero query heads).  decode != 0 selects the small-atom kernel
+// (rank 128, heads dividing 16).  Scratch and atoms as for dsb200_paged_flash_attention with hq = heads.
+DSB_EXPORT int dsb200_paged_flash_latent(const void* q, const void* cache, void* out, const int* tok_seq, const int* tok_pos,
+                                         const int* block_table, int n_tokens, int heads, int rank, int block_size, int max_blocks_per_seq,
+                                         int num_blocks, float scale, int max_atoms, int n_splits, void* scratch, int decode,
+                                         cudaStream_t stream) {
+  using namespace dsb;
+  if (n_tokens == 0) return DSB_OK;
+  DSB_REQUIRE(rank == 64 || rank == 128, "paged_flash_latent: rank %d unsupported (64 or 128)", rank);
+  DSB_REQUIRE(heads >= 1 && 128 % heads == 0, "paged_flash_latent: %d heads must divide 128", heads);
+  DSB_REQUIRE(block_size >= 8 && block_size <= 128 && 128 % block_size == 0, "paged_flash_latent: block size %d must divide 128", block_size);
+  DSB_REQUIRE(max_atoms >= 1 && n_splits >= 1 && n_splits <= 64 && scratch != nullptr, "paged_flash_latent: bad max_atoms / n_splits / scratch");
+  if (decode) {
+    DSB_REQUIRE(rank == 128 && 16 % heads == 0, "paged_flash_latent: the small-atom kernel takes rank 128 and heads dividing 16");
+    return paged::launch_decode(q, cache, out, tok_seq, tok_pos, block_table, n_tokens, heads, 1, block_size, max_blocks_per_seq, num_blocks,
+                                scale, max_atoms, n_splits, scratch, nullptr, 0, stream, heads, 1);
+  }
+  if (rank == 128)
+    return paged::launch<128>(q, cache, out, tok_seq, tok_pos, block_table, n_tokens, heads, 1, block_size, max_blocks_per_seq, num_blocks,
+                              scale, max_atoms, n_splits, scratch, nullptr, 0, stream, heads, 1);
+  return paged::launch<64>(q, cache, out, tok_seq, tok_pos, block_table, n_tokens, heads, 1, block_size, max_blocks_per_seq, num_blocks, scale,
+                           max_atoms, n_splits, scratch, nullptr, 0, stream, heads, 1);
 }

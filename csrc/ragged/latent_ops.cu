@@ -127,7 +127,7 @@ template <typename T>
 __global__ void latent_norm_append_kernel(const T* __restrict__ lat, int ld, const float* __restrict__ wq, const float* __restrict__ wkv,
                                           T* __restrict__ cq, T* __restrict__ cache, const int* __restrict__ tok_seq,
                                           const int* __restrict__ tok_pos, const int* __restrict__ block_table, int bt_stride,
-                                          int block_size, int n_tokens, int nq, int nkv, float eps) {
+                                          int block_size, int cache_ld, int n_tokens, int nq, int nkv, float eps) {
   const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int t = gw >> 1, which = gw & 1;
   if (t >= n_tokens) return;
@@ -139,7 +139,7 @@ __global__ void latent_norm_append_kernel(const T* __restrict__ lat, int ld, con
   if (which) {
     const int pos = tok_pos[t];
     const int blk = block_table[static_cast<size_t>(tok_seq[t]) * bt_stride + pos / block_size];
-    dst = cache + (static_cast<size_t>(blk) * block_size + pos % block_size) * nkv;
+    dst = cache + (static_cast<size_t>(blk) * block_size + pos % block_size) * cache_ld;
   } else {
     dst = cq + static_cast<size_t>(t) * nq;
   }
@@ -533,19 +533,20 @@ DSB_EXPORT int dsb200_sandwich_norm(float* x, const void* y, int y_dtype, const 
 }
 
 // lat [n_tokens, ld] holds (query latent [nq] | key/value latent [nkv]) of every token.  cq [n_tokens, nq] = plain-weight RMS norm
-// of the first part; the RMS-normed second part is written to the token's row of cache [blocks, block_size, nkv].
+// of the first part; the RMS-normed second part is written to the token's row of cache [blocks, block_size, cache_ld] (cache_ld >= nkv:
+// rows may be padded to a width the tensor-core attention takes; the padding is never written).
 DSB_EXPORT int dsb200_latent_norm_append(const void* lat, int ld, const float* wq, const float* wkv, void* cq, void* cache, const int* tok_seq,
-                                         const int* tok_pos, const int* block_table, int bt_stride, int block_size, int n_tokens, int nq,
-                                         int nkv, float eps, int dtype, cudaStream_t stream) {
+                                         const int* tok_pos, const int* block_table, int bt_stride, int block_size, int cache_ld, int n_tokens,
+                                         int nq, int nkv, float eps, int dtype, cudaStream_t stream) {
   if (n_tokens == 0) return DSB_OK;
   const int warps = 2 * n_tokens, wpb = 4;
   const int grid = (warps + wpb - 1) / wpb;
   if (dtype == 0)
     latent_norm_append_kernel<bf16><<<grid, wpb * 32, 0, stream>>>((const bf16*)lat, ld, wq, wkv, (bf16*)cq, (bf16*)cache, tok_seq, tok_pos,
-                                                                  block_table, bt_stride, block_size, n_tokens, nq, nkv, eps);
+                                                                  block_table, bt_stride, block_size, cache_ld, n_tokens, nq, nkv, eps);
   else
     latent_norm_append_kernel<float><<<grid, wpb * 32, 0, stream>>>((const float*)lat, ld, wq, wkv, (float*)cq, (float*)cache, tok_seq, tok_pos,
-                                                                   block_table, bt_stride, block_size, n_tokens, nq, nkv, eps);
+                                                                   block_table, bt_stride, block_size, cache_ld, n_tokens, nq, nkv, eps);
   DSB_CHECK_CUDA(cudaGetLastError());
   return DSB_OK;
 }

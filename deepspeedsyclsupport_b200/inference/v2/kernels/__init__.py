@@ -228,7 +228,8 @@ def moe_gather(moe_out, scores, mapped_slots):
 native.register_sigs({
     "dsb200_embed_sinusoid": "pp i pp p ii p",
     "dsb200_sandwich_norm": "pp i p f p f p i p ii f p",
-    "dsb200_latent_norm_append": "p i pp pp ppp iii ii f i p",
+    "dsb200_latent_norm_append": "p i pp pp ppp iiii ii f i p",
+    "dsb200_paged_flash_latent": "ppp ppp iiiiii f ii p i p",
     "dsb200_latent_attention_scratch_floats": "iiii",
     "dsb200_latent_attention": "p i ll p i p ll p ppp ii iii f i p",
     "dsb200_sigmoid_gate_mul": "p l p l l i i p",
@@ -282,15 +283,40 @@ def sandwich_norm(x, y=None, wb=None, ob=0.0, w=None, o=0.0, eps=1e-6, out_dtype
 
 def latent_norm_append(lat, wq, wkv, cache, tok_seq, tok_pos, block_table, nq, nkv, eps):
     """lat [T, >= nq + nkv]: rows (query latent | key/value latent).  Returns the RMS-normed query latents [T, nq]; the RMS-normed
-    key/value latent of every token is written into cache [blocks, block_size, nkv] at the token's position."""
+    key/value latent of every token is written into cache [blocks, block_size, >= nkv] at the token's position (columns past nkv
+    are padding and are left alone)."""
     T = lat.shape[0]
-    assert lat.stride(1) == 1 and cache.dtype == lat.dtype and cache.is_contiguous() and cache.shape[2] == nkv
+    assert lat.stride(1) == 1 and cache.dtype == lat.dtype and cache.is_contiguous() and cache.shape[2] >= nkv
     cq = torch.empty(T, nq, dtype=lat.dtype, device=lat.device)
     native.check(native.lib().dsb200_latent_norm_append(native.ptr(lat), lat.stride(0), native.ptr(wq), native.ptr(wkv), native.ptr(cq),
                                                         native.ptr(cache), native.ptr(tok_seq), native.ptr(tok_pos), native.ptr(block_table),
-                                                        block_table.stride(0), cache.shape[1], T, nq, nkv, float(eps), _dt(lat),
+                                                        block_table.stride(0), cache.shape[1], cache.shape[2], T, nq, nkv, float(eps), _dt(lat),
                                                         native.stream_ptr()))
     return cq
+
+
+def paged_latent_flash(q_abs, cache, tok_seq, tok_pos, block_table, scale, decode=False, max_context=None, n_splits=None):
+    """`latent_attention` on the tensor cores (csrc/attn/paged_flash.cu with one cache plane serving as keys and values): q_abs
+    [T, heads, rank] bf16 contiguous with heads dividing 128 and rank 64 / 128, cache [blocks, block_size, rank] bf16 with a block size
+    dividing 128.  Returns bf16 [T, heads, rank].  `decode`: (almost) one token per sequence -- the small-atom kernel (rank 128,
+    heads dividing 16)."""
+    T, Hp, R = q_abs.shape
+    bs = cache.shape[1]
+    assert q_abs.is_contiguous() and cache.is_contiguous() and q_abs.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
+    decode = bool(decode) and R == 128 and 16 % Hp == 0
+    nt = (16 if decode else 128) // Hp
+    max_atoms = max(1, min(T, (T + nt - 1) // nt + block_table.shape[0]))
+    if n_splits is None:
+        pages = -(-(max_context if max_context is not None else block_table.shape[1] * bs) // 128)
+        n_splits = _pick_splits(T, Hp, R, max_atoms, pages, page_us=0.45 if decode else 0.7)
+    out = torch.empty(T, Hp, R, dtype=torch.bfloat16, device=q_abs.device)
+    nbytes = native.lib().dsb200_paged_flash_scratch_bytes(T, Hp, R, max_atoms, n_splits)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=q_abs.device)
+    native.check(native.lib().dsb200_paged_flash_latent(native.ptr(q_abs), native.ptr(cache), native.ptr(out), native.ptr(tok_seq),
+                                                        native.ptr(tok_pos), native.ptr(block_table), T, Hp, R, bs, block_table.shape[1],
+                                                        cache.shape[0], float(scale), max_atoms, n_splits, native.ptr(scratch), int(decode),
+                                                        native.stream_ptr()), 2 + (n_splits > 1))
+    return out
 
 
 def _latent_splits(T, head_groups, max_keys):

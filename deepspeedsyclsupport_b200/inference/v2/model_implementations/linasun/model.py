@@ -134,7 +134,7 @@ class LinasunInferenceModel(RaggedTransformer, DSInferenceModelBase):
     # ---- cache: one single-plane layer of kv_rank values per token for every layer run
     def kv_cache_config(self, block_size: int = 64):
         name = {torch.bfloat16: "bf16", torch.float32: "fp32"}[self.dtype]
-        shapes = [(1, 1, self.spec.layers[li].mixer.kv_rank) for li in self._order]
+        shapes = [(1, 1, self.attn_mods[li].cache_rank) for li in self._order]  # kv_rank, padded where the tensor-core kernel wants it
         return KVCacheConfig(block_size=block_size, cache_shape=(len(shapes), 1, max([s[2] for s in shapes] + [1])), cache_dtype=name,
                              layer_shapes=shapes)
 

@@ -145,6 +145,14 @@ int dsb200_paged_flash_decode(const void* qkv, const void* kv_cache, void* out, 
                               const int* block_table, int n_tokens, int hq, int hkv, int head_dim, int block_size,
                               int max_blocks_per_seq, int num_blocks, float scale, int max_atoms, int n_splits,
                               void* scratch, const float* alibi_slopes, int window, dsb200_stream_t stream);
+/* Attention over a paged cache of latents: every one of the `heads` query heads of a token attends to the SAME cached rows, which
+ * serve as keys and as values (one plane per block: cache [num_blocks][block_size][rank], bf16).  q and out are [n_tokens][heads][rank]
+ * bf16; rank 64 or 128; heads must divide 128 (callers pad with zero query heads).  decode != 0 selects the small-atom kernel
+ * (rank 128, heads dividing 16).  Scratch and atoms as for dsb200_paged_flash_attention with hq = heads. */
+int dsb200_paged_flash_latent(const void* q, const void* cache, void* out, const int* tok_seq, const int* tok_pos,
+                              const int* block_table, int n_tokens, int heads, int rank, int block_size,
+                              int max_blocks_per_seq, int num_blocks, float scale, int max_atoms, int n_splits,
+                              void* scratch, int decode, dsb200_stream_t stream);
 
 /* ---- csrc/comm/symm.cu */
 /* ---- allocation / mapping (host pointers unless noted) */
@@ -367,10 +375,12 @@ int dsb200_sandwich_norm(float* x, const void* y, int y_dtype, const float* wb, 
                          void* out, int out_dtype, const int* rows, int n_rows, int dim, float eps,
                          dsb200_stream_t stream);
 /* lat [n_tokens, ld] holds (query latent [nq] | key/value latent [nkv]) of every token.  cq [n_tokens, nq] = plain-weight RMS norm
- * of the first part; the RMS-normed second part is written to the token's row of cache [blocks, block_size, nkv]. */
+ * of the first part; the RMS-normed second part is written to the token's row of cache [blocks, block_size, cache_ld] (cache_ld >= nkv:
+ * rows may be padded to a width the tensor-core attention takes; the padding is never written). */
 int dsb200_latent_norm_append(const void* lat, int ld, const float* wq, const float* wkv, void* cq, void* cache,
                               const int* tok_seq, const int* tok_pos, const int* block_table, int bt_stride,
-                              int block_size, int n_tokens, int nq, int nkv, float eps, int dtype, dsb200_stream_t stream);
+                              int block_size, int cache_ld, int n_tokens, int nq, int nkv, float eps, int dtype,
+                              dsb200_stream_t stream);
 /* floats of scratch `dsb200_latent_attention` needs for n_splits > 1 */
 long long dsb200_latent_attention_scratch_floats(int n_tokens, int H, int R, int n_splits);
 /* out[t, h, :] = sum_j softmax_j(scale * q[t, h, :] . c_j) c_j over the cached latents c_0 .. c_pos(t) of the token's sequence.

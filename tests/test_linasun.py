@@ -161,6 +161,62 @@ def test_latent_attention_over_pages(dt, H, R, block, splits):
 
 
 @gpu
+@pytest.mark.parametrize("H,R,block,decode", [(4, 64, 16, False), (8, 128, 64, False), (16, 128, 128, True), (2, 128, 32, True), (32, 64, 64, False)])
+def test_tensor_core_latent_attention(H, R, block, decode):
+    """The one-plane mode of the paged flash kernels against the oracle's softmax over latents (bf16 operands)."""
+    K = _K()
+    torch.manual_seed(H + R)
+    lens = [block * 2 + 1, 1, 300] if not decode else [block * 2 + 1, 1, 300, 129]
+    c_rows = [torch.randn(n, R).bfloat16() for n in lens]
+    cache, bt = _paged(c_rows, block)
+    cache = torch.nan_to_num(cache, nan=0.0)  # rows past a sequence's end are read (and masked) by the kernel: they must be finite
+    if decode:  # the last token of every sequence
+        tok_seq = torch.arange(len(lens), dtype=torch.int32)
+        tok_pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    else:
+        tok_seq = torch.tensor(sum([[s] * n for s, n in enumerate(lens)], []), dtype=torch.int32)
+        tok_pos = torch.tensor(sum([list(range(n)) for n in lens], []), dtype=torch.int32)
+    q = (torch.randn(len(tok_seq), H, R) * 0.5).bfloat16()
+    got = K.paged_latent_flash(q.cuda(), cache.cuda(), tok_seq.cuda(), tok_pos.cuda(), bt.cuda(), 0.2, decode=decode)
+    for t in range(len(tok_seq)):
+        c = c_rows[int(tok_seq[t])][:int(tok_pos[t]) + 1].double()
+        p = torch.softmax((q[t].double() @ c.T) * 0.2, -1)
+        assert torch.allclose(got[t].cpu().double(), p @ c, rtol=3e-2, atol=3e-2), t
+
+
+@gpu
+def test_tensor_core_latent_attention_finds_one_far_key():
+    K = _K()
+    n, R, H, block = 2048, 64, 8, 64
+    for far in (0, 63, 64, 1500, 2047):
+        c = (torch.randn(n, R) * 0.1).bfloat16()
+        c[far] = (torch.randn(R).sign() * 2.0).bfloat16()
+        q = (c[far].float().repeat(H, 1)[None] * 4.0).bfloat16()
+        cache, bt = _paged([c], block, perm_seed=far)
+        cache = torch.nan_to_num(cache, nan=0.0)
+        z = torch.zeros(1, dtype=torch.int32).cuda()
+        got = K.paged_latent_flash(q.cuda(), cache.cuda(), z, torch.tensor([n - 1], dtype=torch.int32).cuda(), bt.cuda(), 1.0)
+        assert torch.allclose(got.cpu()[0].float(), c[far].float().expand(H, R), atol=2e-2), far
+        if far > 0:
+            got = K.paged_latent_flash(q.cuda(), cache.cuda(), z, torch.tensor([far - 1], dtype=torch.int32).cuda(), bt.cuda(), 1.0)
+            assert (got.cpu()[0].float() - c[far].float()).abs().max() > 1.0, far
+
+
+@gpu
+def test_bf16_model_on_the_cuda_core_attention_too(tmp_path_factory, monkeypatch):
+    """bf16 normally takes the tensor-core attention; with it switched off the general kernel serves the same model."""
+    monkeypatch.setenv("DSB200_LATENT_FLASH", "0")
+    cfg, w, path = _model("aligned", tmp_path_factory)
+    eng = _engine(path, torch.bfloat16)
+    assert not eng.model().attn_mods[0]._flash and eng.model().attn_mods[1].cache_rank == 96
+    toks = _tokens(cfg, 40, 3)
+    want = O.forward(cfg, w, toks.tolist())
+    got = torch.cat([eng.put([1], [toks[:33]], logit_positions=[list(range(33))])] + [eng.put([1], [toks[i:i + 1]]) for i in range(33, 40)])
+    ok, err = _close(got, want, torch.bfloat16)
+    assert ok, err
+
+
+@gpu
 @pytest.mark.parametrize("far", [0, 63, 64, 700, 1023])
 def test_latent_attention_finds_one_far_key(far):
     """One latent far back (also at a page's first and last row) is made to dominate: the output must be that row."""
