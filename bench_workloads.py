@@ -308,4 +308,215 @@ def run_ulysses13b(args):
                                world, args, ms, config, clocks, launches, extra)), flush=True)
 
 
-WORKLOADS = {"fastgen70b": run_fastgen70b, "mixtral": run_mixtral, "ulysses13b": run_ulysses13b}
+
+# ------------------------------------------------------------------------------------------------ Linasun beside Mixtral (FastGen, 1 GPU)
+LINASUN_SIZES = {
+    # name: (width, layers, heads, head dim, kv heads of the Mixtral twin, latent rank, query rank, experts, top, ff, vocab)
+    "s": (2048, 4, 16, 128, 4, 128, 512, 8, 2, 1024, 32000),
+    "m": (4096, 4, 32, 128, 8, 128, 1024, 8, 2, 2048, 32000),
+    "l": (6144, 2, 48, 128, 8, 128, 1536, 16, 4, 2048, 32000),
+}
+
+
+def _linasun_state(torch, dev, W, L, H, d, R, Q, E, top, ff, V):
+    cfg = {"architecture": "Linasun", "vocab": V, "width": W, "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "loop": {"start": 0, "stop": 0, "times": 1},
+           "layers": [{"type": "latent_attention", "mixer": {"heads": H, "dim": d, "vdim": d, "kv_rank": R, "q_rank": Q, "scale": d ** -0.5},
+                       "mlp": {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": E, "top": top, "groups": {"count": 4, "keep": 2}}}}
+                      for _ in range(L)]}
+
+    def r(*shape, std=0.02):
+        return torch.empty(*shape, device=dev, dtype=torch.bfloat16).normal_(0.0, std)
+
+    sd = {"embed": r(V, W, std=1.0), "final.norm": r(W), "head": r(V, W)}
+    for i in range(L):
+        p = f"l{i}."
+        for n in ("norm1", "norm1b", "norm2", "norm2b"):
+            sd[p + n] = r(W)
+        sd.update({p + "mix.dq": r(Q, W), p + "mix.dq.norm": r(Q) + 1, p + "mix.uq": r(H * d, Q), p + "mix.dkv": r(R, W), p + "mix.dkv.norm": r(R) + 1,
+                   p + "mix.uk": r(H * d, R), p + "mix.uv": r(H * d, R), p + "mix.g": r(H * d, W), p + "mix.o": r(W, H * d),
+                   p + "mlp.router": r(E, W, std=0.5), p + "mlp.correction": r(E)})
+        for e in range(E):
+            sd.update({p + f"mlp.e{e}.gate": r(ff, W), p + f"mlp.e{e}.up": r(ff, W), p + f"mlp.e{e}.down": r(W, ff)})
+    return cfg, sd
+
+
+def _mixtral_state(torch, dev, W, L, H, d, hkv, E, top, ff, V):
+    cfg = dict(vocab_size=V, hidden_size=W, intermediate_size=ff, num_hidden_layers=L, num_attention_heads=H, num_key_value_heads=hkv,
+               rms_norm_eps=1e-5, rope_theta=1e6, max_position_embeddings=8192, num_local_experts=E, num_experts_per_tok=top)
+    assert H * d == W, "the Mixtral twin derives its head size from hidden / heads"
+
+    def r(*shape, std=0.02, one=False):
+        t = torch.empty(*shape, device=dev, dtype=torch.bfloat16).normal_(0.0, std)
+        return t + 1 if one else t
+
+    sd = {"model.embed_tokens.weight": r(V, W, std=1.0), "model.norm.weight": r(W, one=True), "lm_head.weight": r(V, W)}
+    for i in range(L):
+        p = f"model.layers.{i}."
+        sd.update({p + "self_attn.q_proj.weight": r(H * d, W), p + "self_attn.k_proj.weight": r(hkv * d, W), p + "self_attn.v_proj.weight": r(hkv * d, W),
+                   p + "self_attn.o_proj.weight": r(W, H * d), p + "block_sparse_moe.gate.weight": r(E, W, std=0.5),
+                   p + "input_layernorm.weight": r(W, one=True), p + "post_attention_layernorm.weight": r(W, one=True)})
+        for e in range(E):
+            sd.update({p + f"block_sparse_moe.experts.{e}.w1.weight": r(ff, W), p + f"block_sparse_moe.experts.{e}.w3.weight": r(ff, W),
+                       p + f"block_sparse_moe.experts.{e}.w2.weight": r(W, ff)})
+    return cfg, sd
+
+
+def _event_ms(torch, fn, iters, flush):
+    """Median device time of fn() over `iters` runs, an L2 flush (a 256 MB write) before every run, 3 warm-up runs."""
+    for _ in range(3):
+        fn()
+    times = []
+    for _ in range(iters):
+        flush.fill_(1.0)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    return sorted(times)[len(times) // 2]
+
+
+def _linasun_kernel_table(torch, peaks, W, H, d, hkv, R, E, top, ff, T, ctx, n_dec):
+    """Every kernel of the new design beside the like kernel of the Mixtral path, isolated, with the fraction of the measured roofline
+    (HBM copy bandwidth for the streaming kernels, cuBLAS bf16 rate for attention prefill)."""
+    from deepspeedsyclsupport_b200.inference.v2 import kernels as K
+    from deepspeedsyclsupport_b200.ops import fused_ops as FO
+    dev = torch.device("cuda")
+    bf = torch.bfloat16
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    rows = []
+
+    def add(name, ms, like, like_ms, nbytes=None, like_bytes=None, flops=None, like_flops=None):
+        def frac(ms_, b, f):
+            return round(max((b or 0) / hbm, (f or 0) / tf) / (ms_ * 1e-3), 3)
+        rows.append({"kernel": name, "ms": round(ms, 4), "roofline_frac": frac(ms, nbytes, flops), "like": like, "like_ms": round(like_ms, 4),
+                     "like_roofline_frac": frac(like_ms, like_bytes if like_bytes is not None else nbytes, like_flops if like_flops is not None else flops)})
+
+    # norms: fused (branch norm + add + next norm) on an fp32 stream vs fused (add + norm) on a bf16 stream
+    x32, y, g32 = torch.randn(T, W, device=dev), torch.randn(T, W, device=dev).to(bf), torch.randn(W, device=dev)
+    xb, gb = torch.randn(T, W, device=dev).to(bf), torch.randn(W, device=dev).to(bf)
+    add("sandwich_norm (fp32 stream)", _event_ms(torch, lambda: K.sandwich_norm(x32, y, g32, 1.0, g32, 1.0, 1e-6), 20, flush),
+        "rms_norm + residual add (bf16 stream)", _event_ms(torch, lambda: FO.rms_norm(y, gb, 1e-5, xb), 20, flush),
+        nbytes=T * W * (4 + 4 + 2 + 2), like_bytes=T * W * (2 + 2 + 2 + 2))
+    # routers
+    lg = torch.randn(T, E, device=dev)
+    corr = torch.randn(E, device=dev)
+    add("grouped_topk_gating", _event_ms(torch, lambda: K.grouped_topk_gating(lg, top, corr, 4, 2), 20, flush),
+        "top_k_gating", _event_ms(torch, lambda: K.top_k_gating(lg, top), 20, flush), nbytes=T * (E * 4 + top * 12))
+    counts, scores, asg, off = K.top_k_gating(lg, top)
+    h = torch.randn(T, W, device=dev).to(bf)
+    add("moe_scatter_rows", _event_ms(torch, lambda: K.moe_scatter_rows(h, counts, asg, off), 20, flush),
+        "moe_scatter", _event_ms(torch, lambda: K.moe_scatter(h, counts, asg, off), 20, flush), nbytes=T * W * 2 * (1 + top))
+    moe_in, cumsum, slots = K.moe_scatter(h, counts, asg, off)
+    dn = torch.randn(T * top, W, device=dev).to(bf)
+    add("moe_gather_rows (fp32 out)", _event_ms(torch, lambda: K.moe_gather_rows(dn, scores, slots), 20, flush),
+        "moe_gather (bf16 out)", _event_ms(torch, lambda: K.moe_gather(dn, scores, slots), 20, flush),
+        nbytes=T * W * (2 * top + 4), like_bytes=T * W * (2 * top + 2))
+    gu = torch.randn(T * top, 2 * ff, device=dev).to(bf)
+    add("clamped_swish_gate", _event_ms(torch, lambda: K.clamped_swish_gate(gu, 1.702, 7.0, 1.0), 20, flush),
+        "gated_act (silu)", _event_ms(torch, lambda: FO.gated_act(gu, "silu"), 20, flush), nbytes=T * top * ff * 6)
+    # attention: one prompt portion of T tokens after ctx cached tokens; then n_dec decode tokens at context ctx
+    bs = 128
+    for label, n_seq, new, seen in (("prefill", max(1, T // 2048), min(T, 2048), ctx), ("decode", n_dec, 1, ctx)):
+        per = -(-(seen + new) // bs)
+        nb = n_seq * per
+        bt = torch.arange(nb, dtype=torch.int32, device=dev).view(n_seq, per)
+        tok_seq = torch.arange(n_seq, dtype=torch.int32, device=dev).repeat_interleave(new)
+        tok_pos = (seen + torch.arange(new, dtype=torch.int32, device=dev)).repeat(n_seq)
+        Tn = n_seq * new
+        lat_cache = torch.randn(nb, bs, R, device=dev).to(bf)
+        Hp = 1 << (H - 1).bit_length()  # the module pads the query heads to a divisor of 128 (useful FLOPs below count H)
+        qa = torch.randn(Tn, Hp, R, device=dev).to(bf)
+        kv = torch.randn(nb, 2, bs, hkv, d, device=dev).to(bf)
+        qkv = torch.randn(Tn, (H + 2 * hkv) * d, device=dev).to(bf)
+        dec = label == "decode"
+        keys = n_seq * (new * seen + new * (new + 1) // 2)  # (query, key) pairs
+        fl_lat, fl_std = 4.0 * keys * H * R, 4.0 * keys * H * d
+        by_lat, by_std = nb * bs * R * 2 + Tn * H * R * 4, nb * bs * hkv * d * 4 + Tn * H * d * 4
+        add(f"latent attention, {label} (tcgen05, one plane)", _event_ms(torch, lambda: K.paged_latent_flash(qa, lat_cache, tok_seq, tok_pos, bt, d ** -0.5, decode=dec), 10, flush),
+            f"paged flash attention, {label} (GQA {H}:{hkv})", _event_ms(torch, lambda: K.paged_attention(qkv, kv, tok_seq, tok_pos, bt, H, hkv, d, d ** -0.5, decode=dec), 10, flush),
+            nbytes=by_lat, like_bytes=by_std, flops=fl_lat, like_flops=fl_std)
+        if label == "decode":
+            qf = qa.float()
+            add("latent attention, decode (CUDA cores, fp32)", _event_ms(torch, lambda: K.latent_attention(qf, lat_cache, tok_seq, tok_pos, bt, d ** -0.5, max_keys=seen + 1), 5, flush),
+                f"paged flash attention, decode (GQA {H}:{hkv})", rows[-1]["like_ms"], nbytes=by_lat, like_bytes=by_std, flops=0, like_flops=0)
+    return rows
+
+
+def run_linasun(args):
+    """Prefill and decode throughput of Linasun through the FastGen engine at a few layer sizes, beside a Mixtral of equal size
+    (same width, layers, heads, experts, ff, top-k, vocabulary), plus the isolated kernels of the new design beside their likes."""
+    sys.path.insert(0, ROOT)
+    import torch
+    import deepspeedsyclsupport_b200 as deepspeed
+    from deepspeedsyclsupport_b200 import comm as dist
+    from deepspeedsyclsupport_b200.inference.v2 import RaggedInferenceEngineConfig, build_engine_from_state_dict
+    from deepspeedsyclsupport_b200.ops import native
+    deepspeed.init_distributed()
+    assert dist.get_world_size() == 1, "--workload linasun is a one-GPU comparison"
+    dev = torch.device("cuda", torch.cuda.current_device())
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")):
+        peaks = dict(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))), source="measured")
+    n_seqs, prompt, budget = min(args.sequences, 64), 1024, 4096
+    results, clocks, l0 = {}, None, native.launch_count
+    g = torch.Generator().manual_seed(11)
+    for name in (args.model.split(",") if args.model != "7b" else ["s", "m", "l"]):
+        W, L, H, d, hkv, R, Q, E, top, ff, V = LINASUN_SIZES[name]
+        max_ctx = -(-(prompt + 4 * (args.steps + args.warmup) * 4 + 64) // 128) * 128
+        ecfg = RaggedInferenceEngineConfig(state_manager={"max_ragged_batch_size": budget, "max_ragged_sequence_count": n_seqs, "max_tracked_sequences": n_seqs,
+                                                          "max_context": max_ctx, "memory_config": {"mode": "allocate", "size": n_seqs * (max_ctx // 128) + 4}})
+        res = {}
+        for fam in ("linasun", "mixtral"):
+            cfg, sd = _linasun_state(torch, dev, W, L, H, d, R, Q, E, top, ff, V) if fam == "linasun" else _mixtral_state(torch, dev, W, L, H, d, hkv, E, top, ff, V)
+            eng = build_engine_from_state_dict(fam, cfg, sd, ecfg, dtype=torch.bfloat16)
+            n_params = sum(v.numel() for v in sd.values())
+            del sd
+            prompts = [torch.randint(0, V, (prompt, ), generator=g).pin_memory() for _ in range(n_seqs)]
+            uids = list(range(n_seqs))
+            state = {"live": False, "next": None}
+
+            def prefill():
+                if state["live"]:
+                    for u in uids:
+                        eng.flush(u)
+                per = budget // prompt
+                nxt = torch.zeros(n_seqs, dtype=torch.long)
+                for i in range(0, n_seqs, per):
+                    us = uids[i:i + per]
+                    nxt[i:i + len(us)] = eng.put(us, [prompts[u] for u in us]).argmax(-1).cpu()
+                state["live"], state["next"] = True, nxt
+
+            def decode():
+                nxt = state["next"]
+                for _ in range(4):
+                    nxt = eng.put(uids, [nxt[u:u + 1] for u in uids]).argmax(-1).cpu()
+                state["next"] = nxt
+
+            ms_p, _ = _timed(torch, dist, prefill, max(1, args.steps // 2), 3)
+            ms_d, clocks = _timed(torch, dist, decode, args.steps, args.warmup)
+            res[fam] = {"params_b": round(n_params / 1e9, 3), "prefill_tokens_per_s": round(n_seqs * prompt / ms_p * 1e3, 1), "prefill_ms": round(ms_p, 2),
+                        "decode_tokens_per_s": round(n_seqs * 4 / ms_d * 1e3, 1), "decode_ms_per_step": round(ms_d / 4, 3)}
+            del eng
+            torch.cuda.empty_cache()
+        res["linasun_over_mixtral"] = {"prefill": round(res["linasun"]["prefill_tokens_per_s"] / res["mixtral"]["prefill_tokens_per_s"], 3),
+                                       "decode": round(res["linasun"]["decode_tokens_per_s"] / res["mixtral"]["decode_tokens_per_s"], 3)}
+        res["shape"] = {"width": W, "layers": L, "heads": H, "head_dim": d, "mixtral_kv_heads": hkv, "kv_rank": R, "q_rank": Q, "experts": E, "top": top, "ff": ff}
+        res["kernels"] = _linasun_kernel_table(torch, peaks, W, H, d, hkv, R, E, top, ff, 4096, 2048, n_seqs)
+        results[name] = res
+    launches = native.launch_count - l0
+    last = results[list(results)[-1]]
+    extra = {"results": results, "peaks": {k: peaks[k] for k in ("hbm_gbs", "bf16_tflops", "source")},
+             "e2e": {"value": last["linasun"]["decode_tokens_per_s"], "unit": "generated tokens/s", "h2d_bytes_per_step": n_seqs * 8, "d2h_bytes_per_step": n_seqs * 8},
+             "reference_arm": "none: the reference has no model of this design"}
+    config = {"model": "linasun (random weights) beside mixtral of equal size", "sizes": list(results), "sequences": n_seqs, "prompt_len": prompt,
+              "token_budget_per_forward": budget, "decode_steps_per_timed_step": 4, "kv_block": 128,
+              "l2_policy": "engine steps: weights exceed the 126 MB L2, no flush; isolated kernels: 256 MB write before every timed run"}
+    print(json.dumps(_line("generated tokens/sec Linasun FastGen ragged decode, 1 GPU (prefill and a Mixtral of equal size alongside)",
+                           last["linasun"]["decode_tokens_per_s"], "tokens/s", 1, args, last["linasun"]["decode_ms_per_step"], config, clocks, launches, extra)),
+          flush=True)
+
+
+WORKLOADS = {"fastgen70b": run_fastgen70b, "mixtral": run_mixtral, "ulysses13b": run_ulysses13b, "linasun": run_linasun}

@@ -121,6 +121,86 @@ __global__ void sandwich_norm_kernel(float* __restrict__ x, const TY* __restrict
   for (int c = threadIdx.x; c < dim; c += blockDim.x) orow[c] = from_f<TO>(xr[c] * inv * (w[c] + o));
 }
 
+// The same for dim % 4 == 0 and dim <= 4 * SN_MAXV * blockDim: 16-byte (fp32) / 8-byte (bf16) accesses, the row is read from global
+// memory once and kept in registers between the statistics and the scaling.
+constexpr int SN_MAXV = 4;
+struct alignas(8) bf16x4 { __nv_bfloat162 a, b; };
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+  const bf16x4 v = *reinterpret_cast<const bf16x4*>(p);
+  const float2 lo = __bfloat1622float2(v.a), hi = __bfloat1622float2(v.b);
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+  bf16x4 o;
+  o.a = __floats2bfloat162_rn(v.x, v.y);
+  o.b = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<bf16x4*>(p) = o;
+}
+
+template <typename TY, typename TO>
+__global__ void sandwich_norm_vec_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ wb, float ob,
+                                         const float* __restrict__ w, float o, TO* __restrict__ out, const int* __restrict__ rows, int dim,
+                                         float eps) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  float* xr = x + static_cast<size_t>(rows ? rows[r] : r) * dim;
+  const int nv = dim >> 2;
+  float4 xv[SN_MAXV];
+  float sx = 0.f;
+  if (y != nullptr) {
+    const TY* yr = y + static_cast<size_t>(r) * dim;
+    float4 yv[SN_MAXV];
+    float sy = 0.f;
+#pragma unroll
+    for (int i = 0; i < SN_MAXV; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < nv) {
+        yv[i] = load4(yr + 4 * c);
+        xv[i] = load4(xr + 4 * c);
+        sy += yv[i].x * yv[i].x + yv[i].y * yv[i].y + yv[i].z * yv[i].z + yv[i].w * yv[i].w;
+      }
+    }
+    sy = block_sum(sy, red);
+    const float inv = 1.f / sqrtf(sy / static_cast<float>(dim) + eps);
+#pragma unroll
+    for (int i = 0; i < SN_MAXV; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < nv) {
+        const float4 g = load4(wb + 4 * c);
+        xv[i].x += yv[i].x * inv * (g.x + ob);
+        xv[i].y += yv[i].y * inv * (g.y + ob);
+        xv[i].z += yv[i].z * inv * (g.z + ob);
+        xv[i].w += yv[i].w * inv * (g.w + ob);
+        store4(xr + 4 * c, xv[i]);
+        sx += xv[i].x * xv[i].x + xv[i].y * xv[i].y + xv[i].z * xv[i].z + xv[i].w * xv[i].w;
+      }
+    }
+  } else if (w != nullptr) {
+#pragma unroll
+    for (int i = 0; i < SN_MAXV; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < nv) {
+        xv[i] = load4(xr + 4 * c);
+        sx += xv[i].x * xv[i].x + xv[i].y * xv[i].y + xv[i].z * xv[i].z + xv[i].w * xv[i].w;
+      }
+    }
+  }
+  if (w == nullptr) return;
+  sx = block_sum(sx, red);
+  const float inv = 1.f / sqrtf(sx / static_cast<float>(dim) + eps);
+  TO* orow = out + static_cast<size_t>(r) * dim;
+#pragma unroll
+  for (int i = 0; i < SN_MAXV; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < nv) {
+      const float4 g = load4(w + 4 * c);
+      store4(orow + 4 * c, make_float4(xv[i].x * inv * (g.x + o), xv[i].y * inv * (g.y + o), xv[i].z * inv * (g.z + o), xv[i].w * inv * (g.w + o)));
+    }
+  }
+}
+
 // One warp per (token, which): which = 0 normalises lat[t, :nq] with wq into cq[t, :]; which = 1 normalises
 // lat[t, nq : nq + nkv] with wkv into the token's row of the paged cache [blocks, block_size, nkv].
 template <typename T>
@@ -310,6 +390,28 @@ __global__ void clamped_swish_gate_kernel(const T* __restrict__ gu, T* __restric
   }
 }
 
+// F % 4 == 0: four outputs per thread and step
+template <typename T>
+__global__ void clamped_swish_gate_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int F, float alpha, float limit,
+                                              float shift) {
+  const int fv = F >> 2;
+  const long long n = rows * fv;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / fv;
+    const int c = static_cast<int>(i % fv) * 4;
+    const float4 g4 = load4(gu + r * 2 * F + c), u4 = load4(gu + r * 2 * F + F + c);
+    const float gs[4] = {g4.x, g4.y, g4.z, g4.w}, us[4] = {u4.x, u4.y, u4.z, u4.w};
+    float o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float g = fminf(gs[k], limit);
+      const float u = fminf(fmaxf(us[k], -limit), limit);
+      o[k] = g * (1.f / (1.f + expf(-alpha * g))) * (u + shift);
+    }
+    store4(out + r * F + c, make_float4(o[0], o[1], o[2], o[3]));
+  }
+}
+
 __global__ void softcap_kernel(float* __restrict__ x, long long ld, int cols, long long n, float cap) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float* p = x + (i / cols) * ld + (i % cols);
@@ -398,7 +500,7 @@ __global__ void expert_cumsum_kernel(const int* __restrict__ counts, long long* 
   }
 }
 
-template <typename T>
+template <typename T, bool VEC>
 __global__ void moe_scatter_kernel(const T* __restrict__ x, const int* __restrict__ assignments, const int* __restrict__ offsets,
                                    const long long* __restrict__ cumsum, T* __restrict__ moe_in, int* __restrict__ mapped_slots, int dim, int K) {
   const int t = blockIdx.x;
@@ -406,18 +508,34 @@ __global__ void moe_scatter_kernel(const T* __restrict__ x, const int* __restric
     const int e = assignments[t * K + k];
     const long long slot = (e == 0 ? 0 : cumsum[e - 1]) + offsets[t * K + k];
     if (threadIdx.x == 0) mapped_slots[t * K + k] = static_cast<int>(slot);
-    for (int c = threadIdx.x; c < dim; c += blockDim.x) moe_in[slot * dim + c] = x[static_cast<size_t>(t) * dim + c];
+    if constexpr (VEC) {
+      for (int c = threadIdx.x * 4; c < dim; c += blockDim.x * 4) store4(moe_in + slot * dim + c, load4(x + static_cast<size_t>(t) * dim + c));
+    } else {
+      for (int c = threadIdx.x; c < dim; c += blockDim.x) moe_in[slot * dim + c] = x[static_cast<size_t>(t) * dim + c];
+    }
   }
 }
 
-template <typename T>
+template <typename T, bool VEC>
 __global__ void moe_gather_kernel(const T* __restrict__ moe_out, const float* __restrict__ scores, const int* __restrict__ mapped_slots,
                                   float* __restrict__ out, int dim, int K) {
   const int t = blockIdx.x;
-  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
-    float acc = 0.f;
-    for (int k = 0; k < K; ++k) acc = fmaf(scores[t * K + k], to_f(moe_out[static_cast<size_t>(mapped_slots[t * K + k]) * dim + c]), acc);
-    out[static_cast<size_t>(t) * dim + c] = acc;
+  if constexpr (VEC) {
+    for (int c = threadIdx.x * 4; c < dim; c += blockDim.x * 4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k < K; ++k) {
+        const float s = scores[t * K + k];
+        const float4 v = load4(moe_out + static_cast<size_t>(mapped_slots[t * K + k]) * dim + c);
+        acc.x = fmaf(s, v.x, acc.x); acc.y = fmaf(s, v.y, acc.y); acc.z = fmaf(s, v.z, acc.z); acc.w = fmaf(s, v.w, acc.w);
+      }
+      store4(out + static_cast<size_t>(t) * dim + c, acc);
+    }
+  } else {
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+      float acc = 0.f;
+      for (int k = 0; k < K; ++k) acc = fmaf(scores[t * K + k], to_f(moe_out[static_cast<size_t>(mapped_slots[t * K + k]) * dim + c]), acc);
+      out[static_cast<size_t>(t) * dim + c] = acc;
+    }
   }
 }
 
@@ -521,8 +639,18 @@ DSB_EXPORT int dsb200_sandwich_norm(float* x, const void* y, int y_dtype, const 
   if (n_rows == 0) return DSB_OK;
   DSB_REQUIRE(y == nullptr || (wb != nullptr && rows == nullptr), "sandwich_norm: a branch needs its weight and cannot be combined with a row gather");
   DSB_REQUIRE(w == nullptr || out != nullptr, "sandwich_norm: an output norm needs an output");
-  const int block = dim >= 1024 ? 256 : 128;
-#define LAUNCH(TY, TO) sandwich_norm_kernel<TY, TO><<<n_rows, block, 0, stream>>>(x, (const TY*)y, wb, ob, w, o, (TO*)out, rows, dim, eps)
+  int block = dim >= 1024 ? 256 : 128;
+  const bool vec = dim % 4 == 0 && dim <= 4 * SN_MAXV * 512 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(wb) |
+                                                                reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  if (vec) {  // one 4-vector per thread and step, at most SN_MAXV steps
+    block = 64;
+    while (block * SN_MAXV * 4 < dim) block *= 2;
+  }
+#define LAUNCH(TY, TO)                                                                                                              \
+  do {                                                                                                                              \
+    if (vec) sandwich_norm_vec_kernel<TY, TO><<<n_rows, block, 0, stream>>>(x, (const TY*)y, wb, ob, w, o, (TO*)out, rows, dim, eps); \
+    else sandwich_norm_kernel<TY, TO><<<n_rows, block, 0, stream>>>(x, (const TY*)y, wb, ob, w, o, (TO*)out, rows, dim, eps);         \
+  } while (0)
   if (y_dtype == 0 && out_dtype == 0) LAUNCH(bf16, bf16);
   else if (y_dtype == 0) LAUNCH(bf16, float);
   else if (out_dtype == 0) LAUNCH(float, bf16);
@@ -558,13 +686,13 @@ DSB_EXPORT long long dsb200_latent_attention_scratch_floats(int n_tokens, int H,
 
 // out[t, h, :] = sum_j softmax_j(scale * q[t, h, :] . c_j) c_j over the cached latents c_0 .. c_pos(t) of the token's sequence.
 // q: bf16 / fp32 (q_dtype 0 / 1) with element strides per token and head; cache [blocks, block_size, R] bf16 / fp32 (cache_dtype);
-// out fp32 with element strides per token and head.  R <= 512.
+// out fp32 with element strides per token and head.  R <= 1024.
 DSB_EXPORT int dsb200_latent_attention(const void* q, int q_dtype, long long q_tok_stride, long long q_head_stride, const void* cache,
                                        int cache_dtype, float* out, long long o_tok_stride, long long o_head_stride, float* scratch,
                                        const int* tok_seq, const int* tok_pos, const int* block_table, int bt_stride, int block_size,
                                        int n_tokens, int H, int R, float scale, int n_splits, cudaStream_t stream) {
   if (n_tokens == 0) return DSB_OK;
-  DSB_REQUIRE(R >= 1 && R <= 512 && H >= 1 && n_splits >= 1, "latent_attention: R=%d (1..512) H=%d splits=%d", R, H, n_splits);
+  DSB_REQUIRE(R >= 1 && R <= 1024 && H >= 1 && n_splits >= 1, "latent_attention: R=%d (1..1024) H=%d splits=%d", R, H, n_splits);
   DSB_REQUIRE(n_splits == 1 || scratch != nullptr, "latent_attention: splits need scratch");
   float* part_ml = scratch;
   float* part_acc = scratch ? scratch + static_cast<size_t>(n_tokens) * n_splits * H * 2 : nullptr;
@@ -583,7 +711,8 @@ DSB_EXPORT int dsb200_latent_attention(const void* q, int q_dtype, long long q_t
     else if (R <= 64) LAUNCH(TC, TQ, 2);       \
     else if (R <= 128) LAUNCH(TC, TQ, 4);      \
     else if (R <= 256) LAUNCH(TC, TQ, 8);      \
-    else LAUNCH(TC, TQ, 16);                   \
+    else if (R <= 512) LAUNCH(TC, TQ, 16);     \
+    else LAUNCH(TC, TQ, 32);                   \
   } while (0)
   if (cache_dtype == 0 && q_dtype == 0) BY_RI(bf16, bf16);
   else if (cache_dtype == 0) BY_RI(bf16, float);
@@ -619,7 +748,12 @@ DSB_EXPORT int dsb200_clamped_swish_gate(const void* gu, void* out, long long ro
                                          cudaStream_t stream) {
   const long long n = rows * F;
   if (n == 0) return DSB_OK;
-  if (dtype == 0)
+  const bool vec = F % 4 == 0 && ((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  if (vec && dtype == 0)
+    clamped_swish_gate_vec_kernel<bf16><<<grid_for(n / 4, 256), 256, 0, stream>>>((const bf16*)gu, (bf16*)out, rows, F, alpha, limit, shift);
+  else if (vec)
+    clamped_swish_gate_vec_kernel<float><<<grid_for(n / 4, 256), 256, 0, stream>>>((const float*)gu, (float*)out, rows, F, alpha, limit, shift);
+  else if (dtype == 0)
     clamped_swish_gate_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((const bf16*)gu, (bf16*)out, rows, F, alpha, limit, shift);
   else
     clamped_swish_gate_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>((const float*)gu, (float*)out, rows, F, alpha, limit, shift);
@@ -663,11 +797,13 @@ DSB_EXPORT int dsb200_moe_scatter_rows(const void* x, const int* expert_counts, 
                                        int top_k, int dtype, cudaStream_t stream) {
   if (n_tokens == 0) return DSB_OK;
   expert_cumsum_kernel<<<1, 32, 0, stream>>>(expert_counts, expert_cumsum, n_experts);
-  if (dtype == 0)
-    moe_scatter_kernel<bf16><<<n_tokens, 128, 0, stream>>>((const bf16*)x, assignments, offsets, expert_cumsum, (bf16*)moe_in, mapped_slots, dim, top_k);
-  else
-    moe_scatter_kernel<float><<<n_tokens, 128, 0, stream>>>((const float*)x, assignments, offsets, expert_cumsum, (float*)moe_in, mapped_slots, dim,
-                                                           top_k);
+  const bool vec = dim % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(moe_in)) & 15) == 0;
+#define LAUNCH(T, V) moe_scatter_kernel<T, V><<<n_tokens, 256, 0, stream>>>((const T*)x, assignments, offsets, expert_cumsum, (T*)moe_in, mapped_slots, dim, top_k)
+  if (dtype == 0 && vec) LAUNCH(bf16, true);
+  else if (dtype == 0) LAUNCH(bf16, false);
+  else if (vec) LAUNCH(float, true);
+  else LAUNCH(float, false);
+#undef LAUNCH
   DSB_CHECK_CUDA(cudaGetLastError());
   return DSB_OK;
 }
@@ -676,10 +812,13 @@ DSB_EXPORT int dsb200_moe_scatter_rows(const void* x, const int* expert_counts, 
 DSB_EXPORT int dsb200_moe_gather_rows(const void* moe_out, const float* scores, const int* mapped_slots, float* out, int n_tokens, int dim,
                                       int top_k, int dtype, cudaStream_t stream) {
   if (n_tokens == 0) return DSB_OK;
-  if (dtype == 0)
-    moe_gather_kernel<bf16><<<n_tokens, 128, 0, stream>>>((const bf16*)moe_out, scores, mapped_slots, out, dim, top_k);
-  else
-    moe_gather_kernel<float><<<n_tokens, 128, 0, stream>>>((const float*)moe_out, scores, mapped_slots, out, dim, top_k);
+  const bool vec = dim % 4 == 0 && ((reinterpret_cast<uintptr_t>(moe_out) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+#define LAUNCH(T, V) moe_gather_kernel<T, V><<<n_tokens, 256, 0, stream>>>((const T*)moe_out, scores, mapped_slots, out, dim, top_k)
+  if (dtype == 0 && vec) LAUNCH(bf16, true);
+  else if (dtype == 0) LAUNCH(bf16, false);
+  else if (vec) LAUNCH(float, true);
+  else LAUNCH(float, false);
+#undef LAUNCH
   DSB_CHECK_CUDA(cudaGetLastError());
   return DSB_OK;
 }

@@ -79,6 +79,6 @@ class DSLatentAttentionConfig(DSModuleConfig):
         for k in ("n_heads", "qk_dim", "v_dim", "kv_rank", "q_rank"):
             if getattr(self, k) <= 0:
                 raise ValueError(f"{k} must be positive")
-        if self.kv_rank > 512:
-            raise ValueError("the latent attention kernels hold a latent row of at most 512 values")
+        if self.kv_rank > 1024:
+            raise ValueError("the latent attention kernels hold a latent row of at most 1024 values")
         return self
