@@ -419,7 +419,7 @@ def _linasun_kernel_table(torch, peaks, W, H, d, hkv, R, E, top, ff, T, ctx, n_d
         "gated_act (silu)", _event_ms(torch, lambda: FO.gated_act(gu, "silu"), 20, flush), nbytes=T * top * ff * 6)
     # attention: one prompt portion of T tokens after ctx cached tokens; then n_dec decode tokens at context ctx
     bs = 128
-    for label, n_seq, new, seen in (("prefill", max(1, T // 2048), min(T, 2048), ctx), ("decode", n_dec, 1, ctx)):
+    for label, n_seq, new, seen in (("prefill", max(1, T // 2048), min(T, 2048), ctx), ("decode", n_dec, 1, ctx), ("decode 16K", n_dec, 1, 8 * ctx)):
         per = -(-(seen + new) // bs)
         nb = n_seq * per
         bt = torch.arange(nb, dtype=torch.int32, device=dev).view(n_seq, per)
@@ -431,15 +431,15 @@ def _linasun_kernel_table(torch, peaks, W, H, d, hkv, R, E, top, ff, T, ctx, n_d
         qa = torch.randn(Tn, Hp, R, device=dev).to(bf)
         kv = torch.randn(nb, 2, bs, hkv, d, device=dev).to(bf)
         qkv = torch.randn(Tn, (H + 2 * hkv) * d, device=dev).to(bf)
-        dec = label == "decode"
+        dec = label.startswith("decode")
         keys = n_seq * (new * seen + new * (new + 1) // 2)  # (query, key) pairs
         fl_lat, fl_std = 4.0 * keys * H * R, 4.0 * keys * H * d
         by_lat, by_std = nb * bs * R * 2 + Tn * H * R * 4, nb * bs * hkv * d * 4 + Tn * H * d * 4
         add(f"latent attention, {label} (tcgen05, one plane)", _event_ms(torch, lambda: K.paged_latent_flash(qa, lat_cache, tok_seq, tok_pos, bt, d ** -0.5, decode=dec), 10, flush),
             f"paged flash attention, {label} (GQA {H}:{hkv})", _event_ms(torch, lambda: K.paged_attention(qkv, kv, tok_seq, tok_pos, bt, H, hkv, d, d ** -0.5, decode=dec), 10, flush),
             nbytes=by_lat, like_bytes=by_std, flops=fl_lat, like_flops=fl_std)
-        if label == "decode":
-            qf = qa.float()
+        if dec:
+            qf = qa[:, :H].float()
             add("latent attention, decode (CUDA cores, fp32)", _event_ms(torch, lambda: K.latent_attention(qf, lat_cache, tok_seq, tok_pos, bt, d ** -0.5, max_keys=seen + 1), 5, flush),
                 f"paged flash attention, decode (GQA {H}:{hkv})", rows[-1]["like_ms"], nbytes=by_lat, like_bytes=by_std, flops=0, like_flops=0)
     return rows

@@ -320,9 +320,10 @@ def paged_latent_flash(q_abs, cache, tok_seq, tok_pos, block_table, scale, decod
 
 
 def _latent_splits(T, head_groups, max_keys):
-    """Key splits per token: fill the SMs when the batch is small and the context long; one split per 512 keys at most."""
+    """Key splits per token for the CUDA-core kernel: its CTAs are small (4 warps, ~20 KB of shared memory), so a decode batch wants
+    about 8 of them per SM to hide the shared-memory latency of the score loop; at least 128 keys per split, at most 32 splits."""
     ctas = max(1, T * head_groups)
-    return max(1, min(-(-max_keys // 512), (2 * 148) // ctas, 32))
+    return max(1, min(-(-max_keys // 128), (8 * 148) // ctas, 32))
 
 
 def latent_attention(q_abs, cache, tok_seq, tok_pos, block_table, scale, out=None, max_keys=None, n_splits=None):
