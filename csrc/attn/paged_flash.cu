@@ -830,14 +830,18 @@ __global__ void combine_splits_kernel(const float* __restrict__ part_o, const fl
 template <int D>
 static int launch(const void* qkv, const void* kv_cache, void* out, const int* tok_seq, const int* tok_pos, const int* block_table,
                   int T, int hq, int hkv, int block_size, int max_blocks, int num_blocks, float scale, int max_atoms, int n_splits,
-                  void* scratch, const float* alibi, int window, cudaStream_t stream, int q_row_heads = 0, int kv_planes = 2) {
+                  void* scratch, const float* alibi, int window, cudaStream_t stream, int q_heads = 0, long long q_head_stride = 0,
+                  long long q_tok_stride = 0, int kv_planes = 2) {
   using SMEM = Smem<D>;
   const int group = hq / hkv, nt_tile = BM / group;
-  const int heads = q_row_heads ? q_row_heads : hq + 2 * hkv;  // heads per row of the query tensor
+  // the query tensor: [T][heads][D] rows of the fused projection by default; callers may give the number of heads that exist (a box
+  // that reaches past them reads zeros) and element strides per head and per token (a head-major [heads][T][D] tensor, say)
+  const int heads = q_heads ? q_heads : hq + 2 * hkv;
+  const uint64_t qhs = q_head_stride ? q_head_stride : D, qts = q_tok_stride ? q_tok_stride : static_cast<uint64_t>(heads) * D;
   CUtensorMap tmQ, tmKV;
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(heads), static_cast<uint64_t>(T)};
-    const uint64_t strides[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(heads) * D * 2};
+    const uint64_t strides[2] = {qhs * 2, qts * 2};
     const uint32_t box[3] = {64, static_cast<uint32_t>(group), static_cast<uint32_t>(nt_tile)};
     int rc = make_tensor_map(&tmQ, TMA_BF16, 3, qkv, dims, strides, box, TMA_SW_128);
     if (rc) return rc;
@@ -902,15 +906,16 @@ static int launch(const void* qkv, const void* kv_cache, void* out, const int* t
 // decode variant: atoms of at most 16 / group tokens, head_dim 128
 static int launch_decode(const void* qkv, const void* kv_cache, void* out, const int* tok_seq, const int* tok_pos, const int* block_table,
                          int T, int hq, int hkv, int block_size, int max_blocks, int num_blocks, float scale, int max_atoms,
-                         int n_splits, void* scratch, const float* alibi, int window, cudaStream_t stream, int q_row_heads = 0,
-                         int kv_planes = 2) {
+                         int n_splits, void* scratch, const float* alibi, int window, cudaStream_t stream, int q_heads = 0,
+                         long long q_head_stride = 0, long long q_tok_stride = 0, int kv_planes = 2) {
   constexpr int D = 128;
   const int group = hq / hkv, nt_tile = NQ / group;
-  const int heads = q_row_heads ? q_row_heads : hq + 2 * hkv;
+  const int heads = q_heads ? q_heads : hq + 2 * hkv;
+  const uint64_t qhs = q_head_stride ? q_head_stride : D, qts = q_tok_stride ? q_tok_stride : static_cast<uint64_t>(heads) * D;
   CUtensorMap tmQ, tmKV;
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(heads), static_cast<uint64_t>(T)};
-    const uint64_t strides[2] = {static_cast<uint64_t>(D) * 2, static_cast<uint64_t>(heads) * D * 2};
+    const uint64_t strides[2] = {qhs * 2, qts * 2};
     const uint32_t box[3] = {64, static_cast<uint32_t>(group), static_cast<uint32_t>(nt_tile)};
     int rc = make_tensor_map(&tmQ, TMA_BF16, 3, qkv, dims, strides, box, TMA_SW_128);
     if (rc) return rc;
@@ -1016,28 +1021,31 @@ DSB_EXPORT int dsb200_paged_flash_decode(const void* qkv, const void* kv_cache, 
                               num_blocks, scale, max_atoms, n_splits, scratch, alibi_slopes, window, stream);
 }
 
-// Attention over a paged cache of latents: every one of the `heads` query heads of a token attends to the SAME cached rows, which
-// serve as keys and as values (one plane per block: cache [num_blocks][block_size][rank], bf16).  q and out are [n_tokens][heads][rank]
-// bf16; rank 64 or 128; heads must divide 128 (callers pad with zero query heads).  decode != 0 selects the small-atom kernel
-// (rank 128, heads dividing 16).  Scratch and atoms as for dsb200_paged_flash_attention with hq = heads.
-DSB_EXPORT int dsb200_paged_flash_latent(const void* q, const void* cache, void* out, const int* tok_seq, const int* tok_pos,
-                                         const int* block_table, int n_tokens, int heads, int rank, int block_size, int max_blocks_per_seq,
-                                         int num_blocks, float scale, int max_atoms, int n_splits, void* scratch, int decode,
-                                         cudaStream_t stream) {
+// Attention over a paged cache of latents: every one of the query heads of a token attends to the SAME cached rows, which serve as
+// keys and as values (one plane per block: cache [num_blocks][block_size][rank], bf16).  q holds q_heads <= heads query heads of
+// `rank` values per token at element strides q_head_stride / q_tok_stride (multiples of 8; token-major [T][heads][rank] or
+// head-major [heads][T][rank]); the kernel works on `heads` heads (a divisor of 128), the ones past q_heads read as zero.
+// out is [n_tokens][heads][rank] bf16; rank 64 or 128.  decode != 0 selects the small-atom kernel (rank 128, heads dividing 16).
+// Scratch and atoms as for dsb200_paged_flash_attention with hq = heads.
+DSB_EXPORT int dsb200_paged_flash_latent(const void* q, int q_heads, long long q_head_stride, long long q_tok_stride, const void* cache,
+                                         void* out, const int* tok_seq, const int* tok_pos, const int* block_table, int n_tokens, int heads,
+                                         int rank, int block_size, int max_blocks_per_seq, int num_blocks, float scale, int max_atoms,
+                                         int n_splits, void* scratch, int decode, cudaStream_t stream) {
   using namespace dsb;
   if (n_tokens == 0) return DSB_OK;
   DSB_REQUIRE(rank == 64 || rank == 128, "paged_flash_latent: rank %d unsupported (64 or 128)", rank);
-  DSB_REQUIRE(heads >= 1 && 128 % heads == 0, "paged_flash_latent: %d heads must divide 128", heads);
+  DSB_REQUIRE(heads >= 1 && 128 % heads == 0 && q_heads >= 1 && q_heads <= heads, "paged_flash_latent: %d (%d given) heads must divide 128", heads, q_heads);
+  DSB_REQUIRE(q_head_stride % 8 == 0 && q_tok_stride % 8 == 0 && q_head_stride > 0 && q_tok_stride > 0, "paged_flash_latent: query strides must be multiples of 8 elements");
   DSB_REQUIRE(block_size >= 8 && block_size <= 128 && 128 % block_size == 0, "paged_flash_latent: block size %d must divide 128", block_size);
   DSB_REQUIRE(max_atoms >= 1 && n_splits >= 1 && n_splits <= 64 && scratch != nullptr, "paged_flash_latent: bad max_atoms / n_splits / scratch");
   if (decode) {
     DSB_REQUIRE(rank == 128 && 16 % heads == 0, "paged_flash_latent: the small-atom kernel takes rank 128 and heads dividing 16");
     return paged::launch_decode(q, cache, out, tok_seq, tok_pos, block_table, n_tokens, heads, 1, block_size, max_blocks_per_seq, num_blocks,
-                                scale, max_atoms, n_splits, scratch, nullptr, 0, stream, heads, 1);
+                                scale, max_atoms, n_splits, scratch, nullptr, 0, stream, q_heads, q_head_stride, q_tok_stride, 1);
   }
   if (rank == 128)
     return paged::launch<128>(q, cache, out, tok_seq, tok_pos, block_table, n_tokens, heads, 1, block_size, max_blocks_per_seq, num_blocks,
-                              scale, max_atoms, n_splits, scratch, nullptr, 0, stream, heads, 1);
+                              scale, max_atoms, n_splits, scratch, nullptr, 0, stream, q_heads, q_head_stride, q_tok_stride, 1);
   return paged::launch<64>(q, cache, out, tok_seq, tok_pos, block_table, n_tokens, heads, 1, block_size, max_blocks_per_seq, num_blocks, scale,
-                           max_atoms, n_splits, scratch, nullptr, 0, stream, heads, 1);
+                           max_atoms, n_splits, scratch, nullptr, 0, stream, q_heads, q_head_stride, q_tok_stride, 1);
 }

@@ -376,6 +376,27 @@ __global__ void sigmoid_gate_mul_kernel(T* __restrict__ a, long long a_ld, const
   }
 }
 
+// out[t, h * dv + c] = a[h, t, c] * sigmoid(g[t, h * dv + c]): the per-head results of a batched GEMM ([H, T, dv], contiguous) become the
+// token-major concatenation of heads, gated, in one pass.  VEC: dv % 4 == 0 and g_ld % 4 == 0.
+template <typename T, bool VEC>
+__global__ void gate_heads_kernel(const T* __restrict__ a, const T* __restrict__ g, long long g_ld, T* __restrict__ out, int n_tokens, int H, int dv) {
+  constexpr int V = VEC ? 4 : 1;
+  const int row = H * dv;
+  const long long n = static_cast<long long>(n_tokens) * row / V;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = i * V;
+    const long long t = e / row;
+    const int rem = static_cast<int>(e % row), h = rem / dv, c = rem % dv;
+    const T* src = a + (static_cast<long long>(h) * n_tokens + t) * dv + c;
+    if constexpr (VEC) {
+      const float4 av = load4(src), gv = load4(g + t * g_ld + rem);
+      store4(out + e, make_float4(av.x / (1.f + expf(-gv.x)), av.y / (1.f + expf(-gv.y)), av.z / (1.f + expf(-gv.z)), av.w / (1.f + expf(-gv.w))));
+    } else {
+      out[e] = from_f<T>(to_f(*src) / (1.f + expf(-to_f(g[t * g_ld + rem]))));
+    }
+  }
+}
+
 // gu [rows, 2 F] = (gate | up) -> out [rows, F]
 template <typename T>
 __global__ void clamped_swish_gate_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int F, float alpha, float limit,
@@ -739,6 +760,26 @@ DSB_EXPORT int dsb200_sigmoid_gate_mul(void* a, long long a_ld, const void* g, l
     sigmoid_gate_mul_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((bf16*)a, a_ld, (const bf16*)g, g_ld, cols, n);
   else
     sigmoid_gate_mul_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>((float*)a, a_ld, (const float*)g, g_ld, cols, n);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// out [n_tokens, H * dv] = heads of a [H, n_tokens, dv] (contiguous) laid side by side per token, times sigmoid(g) with g [n_tokens, H * dv]
+// at row stride g_ld (elements); g may be null (plain transposition).  dtype 0 = bf16, 1 = fp32.
+DSB_EXPORT int dsb200_gate_heads(const void* a, const void* g, long long g_ld, void* out, int n_tokens, int H, int dv, int dtype,
+                                 cudaStream_t stream) {
+  const long long n = static_cast<long long>(n_tokens) * H * dv;
+  if (n == 0) return DSB_OK;
+  DSB_REQUIRE(g != nullptr, "gate_heads: a gate is required");
+  const int esz = dtype == 0 ? 2 : 4;
+  const bool vec = dv % 4 == 0 && g_ld % 4 == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(g) & (4 * esz - 1)) == 0;
+#define LAUNCH(T, V) gate_heads_kernel<T, V><<<grid_for(n / (V ? 4 : 1), 256), 256, 0, stream>>>((const T*)a, (const T*)g, g_ld, (T*)out, n_tokens, H, dv)
+  if (dtype == 0 && vec) LAUNCH(bf16, true);
+  else if (dtype == 0) LAUNCH(bf16, false);
+  else if (vec) LAUNCH(float, true);
+  else LAUNCH(float, false);
+#undef LAUNCH
   DSB_CHECK_CUDA(cudaGetLastError());
   return DSB_OK;
 }

@@ -229,7 +229,8 @@ native.register_sigs({
     "dsb200_embed_sinusoid": "pp i pp p ii p",
     "dsb200_sandwich_norm": "pp i p f p f p i p ii f p",
     "dsb200_latent_norm_append": "p i pp pp ppp iiii ii f i p",
-    "dsb200_paged_flash_latent": "ppp ppp iiiiii f ii p i p",
+    "dsb200_paged_flash_latent": "p i ll pp ppp iiiiii f ii p i p",
+    "dsb200_gate_heads": "pp l p iii i p",
     "dsb200_latent_attention_scratch_floats": "iiii",
     "dsb200_latent_attention": "p i ll p i p ll p ppp ii iii f i p",
     "dsb200_sigmoid_gate_mul": "p l p l l i i p",
@@ -295,14 +296,17 @@ def latent_norm_append(lat, wq, wkv, cache, tok_seq, tok_pos, block_table, nq, n
     return cq
 
 
-def paged_latent_flash(q_abs, cache, tok_seq, tok_pos, block_table, scale, decode=False, max_context=None, n_splits=None):
-    """`latent_attention` on the tensor cores (csrc/attn/paged_flash.cu with one cache plane serving as keys and values): q_abs
-    [T, heads, rank] bf16 contiguous with heads dividing 128 and rank 64 / 128, cache [blocks, block_size, rank] bf16 with a block size
-    dividing 128.  Returns bf16 [T, heads, rank].  `decode`: (almost) one token per sequence -- the small-atom kernel (rank 128,
-    heads dividing 16)."""
-    T, Hp, R = q_abs.shape
+def paged_latent_flash(q_abs, cache, tok_seq, tok_pos, block_table, scale, decode=False, max_context=None, n_splits=None, heads=None):
+    """`latent_attention` on the tensor cores (csrc/attn/paged_flash.cu with one cache plane serving as keys and values).
+    q_abs: bf16 view [T, H, rank] with unit stride in rank and any 16-byte-multiple token / head strides (token-major, or the
+    head-major output of a batched GEMM seen through `.transpose(0, 1)`); rank 64 / 128.  The kernel works on `heads` heads, a divisor
+    of 128 that is >= H (default: the next power of two); heads past H read as zero.  cache [blocks, block_size, rank] bf16 with a
+    block size dividing 128.  Returns bf16 [T, heads, rank] (rows of heads >= H are meaningless).  `decode`: (almost) one token per
+    sequence -- the small-atom kernel (rank 128, heads dividing 16)."""
+    T, H, R = q_abs.shape
+    Hp = heads or (1 << (H - 1).bit_length())
     bs = cache.shape[1]
-    assert q_abs.is_contiguous() and cache.is_contiguous() and q_abs.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
+    assert q_abs.stride(2) == 1 and cache.is_contiguous() and q_abs.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and Hp >= H
     decode = bool(decode) and R == 128 and 16 % Hp == 0
     nt = (16 if decode else 128) // Hp
     max_atoms = max(1, min(T, (T + nt - 1) // nt + block_table.shape[0]))
@@ -312,10 +316,22 @@ def paged_latent_flash(q_abs, cache, tok_seq, tok_pos, block_table, scale, decod
     out = torch.empty(T, Hp, R, dtype=torch.bfloat16, device=q_abs.device)
     nbytes = native.lib().dsb200_paged_flash_scratch_bytes(T, Hp, R, max_atoms, n_splits)
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=q_abs.device)
-    native.check(native.lib().dsb200_paged_flash_latent(native.ptr(q_abs), native.ptr(cache), native.ptr(out), native.ptr(tok_seq),
-                                                        native.ptr(tok_pos), native.ptr(block_table), T, Hp, R, bs, block_table.shape[1],
-                                                        cache.shape[0], float(scale), max_atoms, n_splits, native.ptr(scratch), int(decode),
-                                                        native.stream_ptr()), 2 + (n_splits > 1))
+    native.check(native.lib().dsb200_paged_flash_latent(native.ptr(q_abs), H, q_abs.stride(1) if H > 1 else R, q_abs.stride(0) if T > 1 else H * R,
+                                                        native.ptr(cache), native.ptr(out), native.ptr(tok_seq), native.ptr(tok_pos),
+                                                        native.ptr(block_table), T, Hp, R, bs, block_table.shape[1], cache.shape[0], float(scale),
+                                                        max_atoms, n_splits, native.ptr(scratch), int(decode), native.stream_ptr()),
+                 2 + (n_splits > 1))
+    return out
+
+
+def gate_heads(a, gate):
+    """a [H, T, dv] (contiguous result of a per-head batched GEMM), gate [T, H * dv] (unit column stride) -> [T, H * dv]: the heads
+    side by side per token, times sigmoid(gate), in one pass."""
+    H, T, dv = a.shape
+    assert a.is_contiguous() and gate.shape == (T, H * dv) and gate.stride(1) == 1 and gate.dtype == a.dtype
+    out = torch.empty(T, H * dv, dtype=a.dtype, device=a.device)
+    native.check(native.lib().dsb200_gate_heads(native.ptr(a), native.ptr(gate), gate.stride(0), native.ptr(out), T, H, dv, _dt(a),
+                                                native.stream_ptr()))
     return out
 
 

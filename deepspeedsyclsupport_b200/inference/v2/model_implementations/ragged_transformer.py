@@ -443,7 +443,8 @@ class RaggedTransformer:
         n = batch.current_sequences
         if not (self._graphs_on and n == batch.current_tokens and n > 0 and batch.input_ids().is_cuda):
             return self.forward(batch, state_manager)
-        key = (n, batch.n_logit_rows)  # a step that returns other rows than one per sequence is another launch sequence
+        rows = batch.n_logit_rows  # a step that returns other rows than one per sequence is another launch sequence
+        key = n if rows == n else (n, rows)
         entry = self._graphs.get(key)
         if entry is None:
             seen = self._graph_warm.get(key, 0)

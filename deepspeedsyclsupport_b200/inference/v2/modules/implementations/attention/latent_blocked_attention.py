@@ -116,17 +116,15 @@ class DSLatentBlockedAttention(DSSelfAttentionBase):
         q = dense_matmul(cq, q_up_w).reshape(T, H, c.qk_dim).transpose(0, 1)  # [H, T, qk_dim]
         bs = cache.shape[1]
         if self._flash and bs >= 8 and 128 % bs == 0:
-            Hp = self._heads_p
-            qa = (torch.zeros if Hp > H else torch.empty)(T, Hp, R, dtype=self._dtype, device=latents.device)
-            torch.bmm(q, key_up_w, out=qa[:, :H].transpose(0, 1))  # token-major for the kernel's TMA box; padded heads stay zero
-            att = K.paged_latent_flash(qa, cache, tok_seq, tok_pos, bt, c.scale, decode=batch.current_tokens <= 2 * batch.current_sequences)
+            qa = torch.bmm(q, key_up_w)  # [H, T, R]; the kernel reads it head-major through its TMA strides, missing heads as zeros
+            att = K.paged_latent_flash(qa.transpose(0, 1), cache, tok_seq, tok_pos, bt, c.scale, heads=self._heads_p,
+                                       decode=batch.current_tokens <= 2 * batch.current_sequences)
             o = torch.bmm(att[:, :H].transpose(0, 1), value_up_w)  # [H, T, v_dim]
         else:
             q_abs = _bmm(q, key_up_w, torch.float32)  # [H, T, R]
             att = torch.empty(H, T, R, dtype=torch.float32, device=latents.device)
             K.latent_attention(q_abs.transpose(0, 1), cache, tok_seq, tok_pos, bt, c.scale, out=att.transpose(0, 1))
             o = _bmm(att if self._dtype == torch.float32 else att.to(self._dtype), value_up_w, self._dtype)  # [H, T, v_dim]
-        o = o.transpose(0, 1).reshape(T, H * c.v_dim)
         if gate is not None:
-            K.sigmoid_gate_mul(o, gate)
-        return o
+            return K.gate_heads(o.contiguous(), gate)  # heads side by side per token and the gate, one pass
+        return o.transpose(0, 1).reshape(T, H * c.v_dim)

@@ -145,14 +145,16 @@ int dsb200_paged_flash_decode(const void* qkv, const void* kv_cache, void* out, 
                               const int* block_table, int n_tokens, int hq, int hkv, int head_dim, int block_size,
                               int max_blocks_per_seq, int num_blocks, float scale, int max_atoms, int n_splits,
                               void* scratch, const float* alibi_slopes, int window, dsb200_stream_t stream);
-/* Attention over a paged cache of latents: every one of the `heads` query heads of a token attends to the SAME cached rows, which
- * serve as keys and as values (one plane per block: cache [num_blocks][block_size][rank], bf16).  q and out are [n_tokens][heads][rank]
- * bf16; rank 64 or 128; heads must divide 128 (callers pad with zero query heads).  decode != 0 selects the small-atom kernel
- * (rank 128, heads dividing 16).  Scratch and atoms as for dsb200_paged_flash_attention with hq = heads. */
-int dsb200_paged_flash_latent(const void* q, const void* cache, void* out, const int* tok_seq, const int* tok_pos,
-                              const int* block_table, int n_tokens, int heads, int rank, int block_size,
-                              int max_blocks_per_seq, int num_blocks, float scale, int max_atoms, int n_splits,
-                              void* scratch, int decode, dsb200_stream_t stream);
+/* Attention over a paged cache of latents: every one of the query heads of a token attends to the SAME cached rows, which serve as
+ * keys and as values (one plane per block: cache [num_blocks][block_size][rank], bf16).  q holds q_heads <= heads query heads of
+ * `rank` values per token at element strides q_head_stride / q_tok_stride (multiples of 8; token-major [T][heads][rank] or
+ * head-major [heads][T][rank]); the kernel works on `heads` heads (a divisor of 128), the ones past q_heads read as zero.
+ * out is [n_tokens][heads][rank] bf16; rank 64 or 128.  decode != 0 selects the small-atom kernel (rank 128, heads dividing 16).
+ * Scratch and atoms as for dsb200_paged_flash_attention with hq = heads. */
+int dsb200_paged_flash_latent(const void* q, int q_heads, long long q_head_stride, long long q_tok_stride,
+                              const void* cache, void* out, const int* tok_seq, const int* tok_pos, const int* block_table,
+                              int n_tokens, int heads, int rank, int block_size, int max_blocks_per_seq, int num_blocks,
+                              float scale, int max_atoms, int n_splits, void* scratch, int decode, dsb200_stream_t stream);
 
 /* ---- csrc/comm/symm.cu */
 /* ---- allocation / mapping (host pointers unless noted) */
@@ -385,7 +387,7 @@ int dsb200_latent_norm_append(const void* lat, int ld, const float* wq, const fl
 long long dsb200_latent_attention_scratch_floats(int n_tokens, int H, int R, int n_splits);
 /* out[t, h, :] = sum_j softmax_j(scale * q[t, h, :] . c_j) c_j over the cached latents c_0 .. c_pos(t) of the token's sequence.
  * q: bf16 / fp32 (q_dtype 0 / 1) with element strides per token and head; cache [blocks, block_size, R] bf16 / fp32 (cache_dtype);
- * out fp32 with element strides per token and head.  R <= 512. */
+ * out fp32 with element strides per token and head.  R <= 1024. */
 int dsb200_latent_attention(const void* q, int q_dtype, long long q_tok_stride, long long q_head_stride, const void* cache,
                             int cache_dtype, float* out, long long o_tok_stride, long long o_head_stride, float* scratch,
                             const int* tok_seq, const int* tok_pos, const int* block_table, int bt_stride, int block_size,
@@ -393,6 +395,10 @@ int dsb200_latent_attention(const void* q, int q_dtype, long long q_tok_stride, 
 /* a[r, c] *= sigmoid(g[r, c]) over [rows, cols] with row strides (elements).  dtype 0 = bf16, 1 = fp32. */
 int dsb200_sigmoid_gate_mul(void* a, long long a_ld, const void* g, long long g_ld, long long rows, int cols, int dtype,
                             dsb200_stream_t stream);
+/* out [n_tokens, H * dv] = heads of a [H, n_tokens, dv] (contiguous) laid side by side per token, times sigmoid(g) with g [n_tokens, H * dv]
+ * at row stride g_ld (elements); g may be null (plain transposition).  dtype 0 = bf16, 1 = fp32. */
+int dsb200_gate_heads(const void* a, const void* g, long long g_ld, void* out, int n_tokens, int H, int dv, int dtype,
+                      dsb200_stream_t stream);
 /* gu [rows, 2 F] = (gate | up) -> out [rows, F] = g' * sigmoid(alpha g') * (clamp(u, -limit, limit) + shift), g' = min(g, limit) */
 int dsb200_clamped_swish_gate(const void* gu, void* out, long long rows, int F, float alpha, float limit, float shift,
                               int dtype, dsb200_stream_t stream);

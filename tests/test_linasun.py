@@ -458,3 +458,44 @@ def test_greedy_generation_through_the_scheduler(tmp_path_factory):
     done = sched.run_to_completion()
     for u, p in prompts.items():
         assert done[u] == O.greedy(cfg, w, p.tolist(), 6), u
+
+
+@gpu
+def test_trace_runner_replays_steps(tmp_path_factory):
+    """bin/trace_run as a process: portions of three requests beside single tokens, a request that pauses for a step, wanted
+    positions anywhere in a portion, requests ending at different steps with their pages reused by a later one (pool of 3 pages)."""
+    import json
+    import subprocess
+    cfg, w, path = _model("odd", tmp_path_factory)
+    out_dir = str(tmp_path_factory.mktemp("trace_out"))
+    reqs = {"a": _tokens(cfg, 70, 31).tolist(), "b": _tokens(cfg, 9, 32).tolist(), "c": _tokens(cfg, 64, 33).tolist(), "d": _tokens(cfg, 100, 34).tolist()}
+    want = {k: O.forward(cfg, w, v) for k, v in reqs.items()}
+    plan = [[("a", 30, [0, 29]), ("b", 8, [3])], [("a", 2, [1]), ("c", 64, [63])], [("a", 37, [36]), ("b", 1, [0])], [("a", 1, [0]), ("d", 64, [])],
+            [("d", 2, [0, 1])], [("d", 1, [])], [("d", 33, [32])]]
+    at = {k: 0 for k in reqs}
+    lines, expect = [], []
+    for n, step in enumerate(plan):
+        entries, end, rows = [], [], []
+        for k, cnt, wanted in step:
+            entries.append({"id": k, "tokens": reqs[k][at[k]:at[k] + cnt], "want": wanted})
+            rows += [want[k][at[k] + p] for p in wanted]
+            at[k] += cnt
+            if at[k] == len(reqs[k]):
+                end.append(k)
+        lines.append(json.dumps({"step": n, "entries": entries, "end": end}))
+        expect.append(torch.stack(rows) if rows else None)
+    assert all(at[k] == len(v) for k, v in reqs.items())
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    # live tokens never exceed 192 = three 64-token pages: a (70 -> 2 pages) + b (1 page), then a + c, then d alone (2 pages)
+    r = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", path, "--dtype", "float32", "--out", out_dir, "--max-tokens", "192"],
+                       input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done ")] == [f"done {n}" for n in range(len(plan))]
+    for n, e in enumerate(expect):
+        f = os.path.join(out_dir, f"{n}.f32")
+        if e is None:
+            assert not os.path.exists(f)
+            continue
+        got = torch.frombuffer(bytearray(open(f, "rb").read()), dtype=torch.float32).view(len(e), cfg["vocab"])
+        ok, err = _close(got, e, torch.float32)
+        assert ok, (n, err)
