@@ -103,7 +103,7 @@ def test_embedding_with_sinusoid(dim):
 
 @gpu
 @pytest.mark.parametrize("dt", DTYPES)
-@pytest.mark.parametrize("dim", [5, 320, 1030])
+@pytest.mark.parametrize("dim", [5, 328, 1030])
 def test_sandwich_norm_modes(dt, dim):
     K = _K()
     T, eps = 9, 1e-4
@@ -256,7 +256,7 @@ def test_latent_norm_and_append(dt):
 
 
 @gpu
-@pytest.mark.parametrize("E,top,G,keep", [(8, 4, 2, 1), (6, 2, 3, 2), (12, 1, 1, 1), (16, 5, 4, 4), (9, 3, 3, 1), (64, 8, 8, 3)])
+@pytest.mark.parametrize("E,top,G,keep", [(8, 3, 2, 1), (6, 2, 3, 2), (12, 1, 1, 1), (16, 5, 4, 4), (9, 3, 3, 1), (64, 8, 8, 3)])
 def test_grouped_router(E, top, G, keep):
     K = _K()
     torch.manual_seed(E + top)
