@@ -444,6 +444,8 @@ def test_long_decoding_through_the_step_graphs(tmp_path_factory):
             keep.append(i)
     ok, err = _close(torch.cat(got), want[keep], torch.float32)
     assert ok, err
+    graphs = eng.model()._graphs  # both kinds of step (one logit row, none) were captured and replayed
+    assert 1 in graphs and (1, 0) in graphs, list(graphs)
 
 
 @gpu
