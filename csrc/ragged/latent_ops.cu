@@ -234,9 +234,10 @@ __global__ void latent_norm_append_kernel(const T* __restrict__ lat, int ld, con
 }
 
 // ----------------------------------------------------------------------------------------------------------- latent attention
-// Grid (token, split, head group of 8).  4 warps; warp w owns heads hg*8 + w and hg*8 + w + 4.  Keys come in tiles of 32 rows of
-// the latent cache, converted to fp32 in shared memory (row stride R + 1); lane j scores key j of the tile, then lane l
-// accumulates output columns l, l + 32, ...  RI = ceil(R / 32) columns per lane.
+// Grid (token, split, head group of 8).  4 warps; warp w owns heads hg*8 + w and hg*8 + w + 4 and handles both in one pass, so that
+// every latent value read from shared memory feeds two FMAs.  Keys come in tiles of 32 rows of the latent cache, converted to fp32 in
+// shared memory (row stride R + 1); lane j scores key j of the tile, then lane l accumulates output columns l, l + 32, ...
+// RI = ceil(R / 32) columns per lane.
 constexpr int LA_KT = 32;
 constexpr int LA_HPC = 8;  // heads per CTA
 
@@ -284,30 +285,46 @@ latent_attention_kernel(const TQ* __restrict__ q, long long q_tok_stride, long l
     }
     __syncthreads();
     const bool valid = kt + lane < k1;
-#pragma unroll
-    for (int a = 0; a < 2; ++a) {
-      const int hl = warp + 4 * a;
-      if (h_base + hl >= H) continue;  // warp-uniform
-      const float* qh = q_s + hl * R;
+    // both heads of the warp in one pass over the tile: every latent value read from shared memory feeds two FMAs
+    if (h_base + warp < H) {
+      const float* q0 = q_s + warp * R;
+      const float* q1 = q_s + (warp + 4) * R;  // zeros when the head does not exist
       const float* cj = c_s + lane * RS;
-      float s = 0.f;
-      for (int r = 0; r < R; ++r) s = fmaf(qh[r], cj[r], s);
-      s = valid ? s : -INFINITY;
-      const float mn = fmaxf(m[a], warp_max(s));  // finite: every tile holds at least one visible key
-      const float p = valid ? expf(s - mn) : 0.f;
-      const float corr = expf(m[a] - mn);         // exp(-inf) = 0 on the first tile
-      l[a] = l[a] * corr + warp_sum(p);
-      m[a] = mn;
-      float* pw = p_s + (warp * 2 + a) * LA_KT;
-      pw[lane] = p;
+      float s0 = 0.f, s1 = 0.f;
+      for (int r = 0; r < R; ++r) {
+        const float cv = cj[r];
+        s0 = fmaf(q0[r], cv, s0);
+        s1 = fmaf(q1[r], cv, s1);
+      }
+      s0 = valid ? s0 : -INFINITY;
+      s1 = valid ? s1 : -INFINITY;
+      const float mn0 = fmaxf(m[0], warp_max(s0)), mn1 = fmaxf(m[1], warp_max(s1));  // finite: every tile holds a visible key
+      const float p0 = valid ? expf(s0 - mn0) : 0.f, p1 = valid ? expf(s1 - mn1) : 0.f;
+      const float corr0 = expf(m[0] - mn0), corr1 = expf(m[1] - mn1);  // exp(-inf) = 0 on the first tile
+      l[0] = l[0] * corr0 + warp_sum(p0);
+      l[1] = l[1] * corr1 + warp_sum(p1);
+      m[0] = mn0;
+      m[1] = mn1;
+      float* pw = p_s + warp * 2 * LA_KT;  // [key][2 heads]
+      pw[2 * lane] = p0;
+      pw[2 * lane + 1] = p1;
       __syncwarp();
 #pragma unroll
       for (int i = 0; i < RI; ++i) {
-        const int r = lane + 32 * i;
-        if (r < R) {
-          float o = acc[a][i] * corr;
-          for (int j = 0; j < LA_KT; ++j) o = fmaf(pw[j], c_s[j * RS + r], o);
-          acc[a][i] = o;
+        acc[0][i] *= corr0;
+        acc[1][i] *= corr1;
+      }
+      for (int j = 0; j < LA_KT; ++j) {
+        const float2 pj = *reinterpret_cast<const float2*>(pw + 2 * j);
+        const float* crow = c_s + j * RS;
+#pragma unroll
+        for (int i = 0; i < RI; ++i) {
+          const int r = lane + 32 * i;
+          if (r < R) {
+            const float cv = crow[r];
+            acc[0][i] = fmaf(pj.x, cv, acc[0][i]);
+            acc[1][i] = fmaf(pj.y, cv, acc[1][i]);
+          }
         }
       }
       __syncwarp();

@@ -200,6 +200,13 @@ def test_tensor_core_latent_attention_finds_one_far_key():
         if far > 0:
             got = K.paged_latent_flash(q.cuda(), cache.cuda(), z, torch.tensor([far - 1], dtype=torch.int32).cuda(), bt.cuda(), 1.0)
             assert (got.cpu()[0].float() - c[far].float()).abs().max() > 1.0, far
+        lo, hi = max(far - 2, 0), min(far + 3, n)  # a prompt portion across the key
+        pos = torch.arange(lo, hi, dtype=torch.int32)
+        got = K.paged_latent_flash(q.expand(len(pos), H, R).contiguous().cuda(), cache.cuda(), torch.zeros(len(pos), dtype=torch.int32).cuda(), pos.cuda(),
+                                   bt.cuda(), 1.0)
+        for i, p_ in enumerate(pos.tolist()):
+            seen = torch.allclose(got.cpu()[i].float(), c[far].float().expand(H, R), atol=2e-2)
+            assert seen == (p_ >= far), (far, p_)
 
 
 @gpu
@@ -232,6 +239,13 @@ def test_latent_attention_finds_one_far_key(far):
     if far > 0:  # the key just after the last visible position must not be seen
         got = K.latent_attention(q.cuda(), cache.cuda(), torch.zeros(1, dtype=torch.int32).cuda(), torch.tensor([far - 1], dtype=torch.int32).cuda(), bt.cuda(), 1.0)
         assert (got.cpu()[0] - c[far]).abs().max() > 1.0
+    # the same inside a prompt portion that starts before the key and runs past it: rows before it do not see it, rows from it on do
+    lo, hi = max(far - 2, 0), min(far + 3, n)
+    pos = torch.arange(lo, hi, dtype=torch.int32)
+    got = K.latent_attention(q.expand(len(pos), H, R).contiguous().cuda(), cache.cuda(), torch.zeros(len(pos), dtype=torch.int32).cuda(), pos.cuda(), bt.cuda(), 1.0)
+    for i, p_ in enumerate(pos.tolist()):
+        seen = torch.allclose(got.cpu()[i], c[far].expand(H, R), atol=1e-5)
+        assert seen == (p_ >= far), (far, p_)
 
 
 @gpu
