@@ -495,7 +495,7 @@ def run_linasun(args):
                     nxt = eng.put(uids, [nxt[u:u + 1] for u in uids]).argmax(-1).cpu()
                 state["next"] = nxt
 
-            ms_p, _ = _timed(torch, dist, prefill, max(1, args.steps // 2), 3)
+            ms_p, _ = _timed(torch, dist, prefill, args.steps, 3)
             ms_d, clocks = _timed(torch, dist, decode, args.steps, args.warmup)
             res[fam] = {"params_b": round(n_params / 1e9, 3), "prefill_tokens_per_s": round(n_seqs * prompt / ms_p * 1e3, 1), "prefill_ms": round(ms_p, 2),
                         "decode_tokens_per_s": round(n_seqs * 4 / ms_d * 1e3, 1), "decode_ms_per_step": round(ms_d / 4, 3)}
