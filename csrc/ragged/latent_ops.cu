@@ -11,8 +11,8 @@
 //   latent_attention      softmax(q_abs . c) c over the paged latent cache: all heads of a token share the cached rows
 //                         (keys and values are the same row), causal, split along the keys + merge
 //   sigmoid_gate_mul      a *= sigmoid(g)
-//   grouped_topk_gating   softmax scores (+ correction for the choice only), best `keep` of `groups` neighbour groups by
-//                         their largest choice score, top-k of the surviving experts, weights = uncorrected scores
+//   grouped_topk_gating   softmax scores (+ correction for the selection only), best `keep` of `groups` contiguous expert groups by
+//                         their largest selection score, top-k of the surviving experts, weights = uncorrected scores
 //   moe_scatter / moe_gather   expert-sorted copies and the weighted fp32 combine, any width
 //   clamped_swish_gate    min(g, L) * sigmoid(alpha * min(g, L)) * (clamp(u, -L, L) + shift)
 //   moe_gemm_rows         grouped expert GEMM on CUDA cores (fp32 accumulation) for shapes / dtypes the tensor-core
@@ -458,7 +458,7 @@ __global__ void softcap_kernel(float* __restrict__ x, long long ld, int cols, lo
 }
 
 // ---------------------------------------------------------------------------------------------------------------------- router
-// One warp per token.  Shared memory per warp: E choice scores + G group scores.  Ties go to the lower index.
+// One warp per token.  Shared memory per warp: E selection scores + G group scores.  Ties go to the lower index.
 __global__ void grouped_topk_gating_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int* __restrict__ expert_counts,
                                            float* __restrict__ scores, int* __restrict__ assignments, int* __restrict__ offsets, int n_tokens,
                                            int E, int K, int G, int keep, int normalize) {
@@ -828,9 +828,9 @@ DSB_EXPORT int dsb200_softcap(float* x, long long ld, long long rows, int cols, 
   return DSB_OK;
 }
 
-// Router: softmax over the E logits of a token; choice score = score + correction[e] (correction may be null); experts are split
-// into `groups` equal neighbour groups, of which the `keep` with the largest maximal choice score stay selectable; the top_k
-// selectable experts by choice score are assigned; their weights are the uncorrected scores (divided by their sum when
+// Router: softmax over the E logits of a token; selection score = score + correction[e] (correction may be null); experts are split
+// into `groups` contiguous groups of equal size, of which the `keep` with the largest maximal selection score stay selectable; the top_k
+// selectable experts by selection score are assigned; their weights are the uncorrected scores (divided by their sum when
 // `normalize`).  Outputs as dsb200_top_k_gating; expert_counts must be zeroed by the caller.
 DSB_EXPORT int dsb200_grouped_topk_gating(const float* logits, const float* correction, int* expert_counts, float* scores, int* assignments,
                                           int* offsets, int n_tokens, int n_experts, int top_k, int groups, int keep, int normalize,

@@ -390,7 +390,7 @@ def softcap_(logits, cap):
 
 
 def grouped_topk_gating(logits, k, correction=None, groups=1, keep=1, normalize=False):
-    """Router with a choice correction and neighbour groups (see csrc/ragged/latent_ops.cu).  logits [T, E] fp32 ->
+    """Router with a selection bias and contiguous expert groups (see csrc/ragged/latent_ops.cu).  logits [T, E] fp32 ->
     (expert_counts [E] int32, scores [T, k] fp32, assignments [T, k] int32, offsets [T, k] int32), as `top_k_gating`."""
     assert logits.dtype == torch.float32 and logits.is_cuda and logits.is_contiguous()
     T, E = logits.shape

@@ -2,7 +2,7 @@
 
 A layer's tensors are `l<i>.norm1 / norm1b / norm2 / norm2b`, `l<i>.mix.{dq, dq.norm, uq, dkv, dkv.norm, uk, uv, g, o}` and,
 when the layer has a feed-forward, `l<i>.mlp.{router, correction, e<j>.gate, e<j>.up, e<j>.down}`; outside the layers `embed`,
-`final.norm` and `head`.  Linear weights are stored [out, in]."""
+`final.norm` and `head`.  Linear weights have shape [out, in]."""
 from typing import Optional
 
 import torch

@@ -1,6 +1,6 @@
 """Linasun: a decoder-only family built from
   * an fp32 residual stream that starts as token embedding + sinusoidal position vector,
-  * blocks that RMS-norm every sublayer on both sides, x += norm_b(sublayer(norm_a(x))), with weights stored around zero,
+  * blocks that RMS-norm every sublayer on both sides, x += norm_b(sublayer(norm_a(x))), with zero-centred weights (applied as 1 + w),
   * a latent-attention mixer: queries through a normed low-rank latent, keys and values as per-head up-projections of ONE cached
     normed latent per token, no positional rotation, causal softmax, a sigmoid output gate computed from the mixer's input,
   * an optional mixture-of-experts feed-forward with a grouped, correction-biased top-k router and a clamped gated activation,
@@ -26,7 +26,7 @@ from ..ragged_transformer import RaggedTransformer
 SINUSOID_BASE = 10000.0  # fixed by the design
 SWISH_ALPHA = 1.702  # fixed by the design: experts compute g * sigmoid(1.702 g) * (u + 1)
 UP_SHIFT = 1.0
-NORM_WEIGHT_OFFSET = 1.0  # block norms and the final norm store their weight around zero; the latent norms store it plainly
+NORM_WEIGHT_OFFSET = 1.0  # block norms and the final norm keep a zero-centred weight; the latent norms store it plainly
 
 
 @dataclass

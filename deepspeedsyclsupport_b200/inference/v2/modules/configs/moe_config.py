@@ -12,9 +12,9 @@ class DSMoEConfig(DSModuleConfig):
     output_dtype: DtypeEnum = DtypeEnum.fp16
     activation: ActivationType = ActivationType.IDENTITY
     normalize_scores: bool = False
-    # router with a choice correction and neighbour groups ("grouped_topk_moe"): experts form n_groups equal groups of neighbours,
-    # only the keep_groups groups with the largest best choice score stay selectable; use_correction adds a per-expert term to the
-    # scores for the choice only (the combine weights stay the plain softmax scores)
+    # router with a selection bias and contiguous expert groups ("grouped_topk_moe"): experts form n_groups contiguous groups of equal size,
+    # only the keep_groups groups with the largest best selection score stay selectable; use_correction adds a per-expert term to the
+    # scores for the selection only (the combine weights stay the plain softmax scores)
     n_groups: int = 1
     keep_groups: int = 1
     use_correction: bool = False

@@ -14,7 +14,7 @@ class DSNormConfig(DSModuleConfig):
     residual_dtype: DtypeEnum = DtypeEnum.fp16
     input_dtype: DtypeEnum = DtypeEnum.fp16
     output_dtype: DtypeEnum = DtypeEnum.fp16
-    # norms whose weight is stored around zero multiply by (weight + weight_offset)
+    # norms whose weight is zero-centred multiply by (weight + weight_offset)
     weight_offset: float = 0.0
     # "sandwich" blocks norm a sublayer's output before it is added to the residual: x += norm(branch) * (w_b + offset), and the
     # same pass produces the next sublayer's input norm(x) * (w + offset).  The residual stream is then kept in fp32.

@@ -12,6 +12,6 @@ class DSUnembedConfig(DSModuleConfig):
     max_sequences: int
     vocab_size: int
     eps: float = 1e-5
-    norm_weight_offset: float = 0.0  # the final norm multiplies by (weight + offset): 1.0 for weights stored around zero
+    norm_weight_offset: float = 0.0  # the final norm multiplies by (weight + offset): 1.0 for zero-centred weights (applied as 1 + w)
     logit_softcap: float = 0.0  # > 0: logits <- cap * tanh(logits / cap)
     residual_fp32: bool = False  # the hidden states arrive as the fp32 residual stream; logits leave in fp32

@@ -1,7 +1,7 @@
 """Mixture-of-experts MLP with a grouped, bias-corrected top-k router and a clamped gated activation.
 
-Router (fp32): scores = softmax(W_r h) over all experts; the CHOICE uses scores + correction, restricted to the `keep_groups`
-groups of neighbouring experts whose best choice score is largest; the combine WEIGHTS are the plain scores of the chosen
+Router (fp32): scores = softmax(W_r h) over all experts; the SELECTION uses scores + correction, restricted to the `keep_groups`
+contiguous expert groups whose best selection score is largest; the combine WEIGHTS are the plain scores of the chosen
 experts (optionally renormalised).  Experts: two grouped GEMMs over the rows sorted by expert with the gated activation
 between them; the weighted combine leaves in fp32 (it feeds an fp32 norm / residual).
 

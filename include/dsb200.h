@@ -404,9 +404,9 @@ int dsb200_clamped_swish_gate(const void* gu, void* out, long long rows, int F, 
                               int dtype, dsb200_stream_t stream);
 /* x[r, c] = cap * tanh(x[r, c] / cap) over fp32 [rows, cols] with row stride ld */
 int dsb200_softcap(float* x, long long ld, long long rows, int cols, float cap, dsb200_stream_t stream);
-/* Router: softmax over the E logits of a token; choice score = score + correction[e] (correction may be null); experts are split
- * into `groups` equal neighbour groups, of which the `keep` with the largest maximal choice score stay selectable; the top_k
- * selectable experts by choice score are assigned; their weights are the uncorrected scores (divided by their sum when
+/* Router: softmax over the E logits of a token; selection score = score + correction[e] (correction may be null); experts are split
+ * into `groups` contiguous groups of equal size, of which the `keep` with the largest maximal selection score stay selectable; the top_k
+ * selectable experts by selection score are assigned; their weights are the uncorrected scores (divided by their sum when
  * `normalize`).  Outputs as dsb200_top_k_gating; expert_counts must be zeroed by the caller. */
 int dsb200_grouped_topk_gating(const float* logits, const float* correction, int* expert_counts, float* scores,
                                int* assignments, int* offsets, int n_tokens, int n_experts, int top_k, int groups,

@@ -1,7 +1,7 @@
 """Plain, slow float64 statement of the Linasun design, one function per mechanism, used as the oracle of tests/test_linasun.py.
 Nothing here imports the package under test.
 
-Notation: x is the residual stream [n, width]; W x means x @ W.T for a weight stored [out, in]; positions count from 0."""
+Notation: x is the residual stream [n, width]; a linear weight has shape [out, in] and acts as x @ W.T; position indices are zero-based."""
 import json
 import math
 import os
@@ -12,12 +12,12 @@ F64 = torch.float64
 
 
 def rms_unit(x, eps):
-    """x divided by its root mean square (eps inside the root)."""
+    """x scaled to unit RMS; eps joins the mean square before the square root is taken."""
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
 
 
 def block_norm(x, w, eps):
-    """Norm of the blocks and of the output: weight stored around zero."""
+    """Norm of the blocks and of the output: zero-centred weight (applied as 1 + w)."""
     return rms_unit(x, eps) * (1.0 + w)
 
 

@@ -275,7 +275,7 @@ def test_grouped_router(E, top, G, keep):
     K = _K()
     torch.manual_seed(E + top)
     z = (torch.randn(40, E) * 2).cuda()
-    corr = torch.randn(E).cuda() * 0.5 - 0.6  # mostly negative choice scores: an excluded group must count as -inf, not 0
+    corr = torch.randn(E).cuda() * 0.5 - 0.6  # mostly negative selection scores: an excluded group must count as -inf, not 0
     counts, scores, asg, off = K.grouped_topk_gating(z, top, corr, G, keep)
     chosen, weights = O.route(z.cpu().double(), corr.cpu().double(), top, G, keep)
     assert torch.equal(asg.cpu().long(), chosen) and torch.allclose(scores.cpu().double(), weights, rtol=1e-5, atol=1e-7)
@@ -358,7 +358,7 @@ def _engine(path, dt, pool_tokens=256, block=16, max_seqs=4):
 
 def _close(got, want, dt):
     """Logit rows agree up to a per-row shift, relative to the spread of the logits.  fp32: every row, tightly.  bf16: rounding
-    can flip a close expert choice of a random router for single tokens, so the bound is on the median and the 90th percentile."""
+    can flip a close expert selection of a random router for single tokens, so the bound is on the median and the 90th percentile."""
     d = got.cpu().double() - want
     d = d - d.mean(-1, keepdim=True)
     err = d.pow(2).mean(-1).sqrt() / want.std()
@@ -388,7 +388,7 @@ def test_whole_prompt_and_every_layer(name, dt, tmp_path_factory):
         if dt == torch.float32:
             assert torch.allclose(a.cpu().double(), b, rtol=1e-4, atol=1e-4), f"layer run {r}"
         else:
-            row = (a.cpu().double() - b).norm(dim=-1) / b.norm(dim=-1)  # a flipped close expert choice spoils single rows only
+            row = (a.cpu().double() - b).norm(dim=-1) / b.norm(dim=-1)  # a flipped close expert selection spoils single rows only
             assert float(row.median()) < 2e-2, f"layer run {r}"
     ok, err = _close(got, want, dt)
     assert ok, err
