@@ -85,11 +85,11 @@ __global__ void embed_sinusoid_kernel(const long long* __restrict__ ids, const T
 // --------------------------------------------------------------------------------------------------------------------- norms
 // Row r of the fp32 residual (row rows[r] when `rows` is given; then nothing is written back to x):
 //   y given:   x <- x + y / sqrt(mean(y^2) + eps) * (wb + ob)
-//   w given:   out <- x / sqrt(mean(x^2) + eps) * (w + o)
+//   w given:   out <- x / sqrt(mean(x^2) + eps) * (w + o)      (and the same values unrounded into out32 when that is given)
 template <typename TY, typename TO>
 __global__ void sandwich_norm_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ wb, float ob,
-                                     const float* __restrict__ w, float o, TO* __restrict__ out, const int* __restrict__ rows, int dim,
-                                     float eps) {
+                                     const float* __restrict__ w, float o, TO* __restrict__ out, float* __restrict__ out32,
+                                     const int* __restrict__ rows, int dim, float eps) {
   __shared__ float red[33];
   const int r = blockIdx.x;
   float* xr = x + static_cast<size_t>(rows ? rows[r] : r) * dim;
@@ -118,7 +118,12 @@ __global__ void sandwich_norm_kernel(float* __restrict__ x, const TY* __restrict
   sx = block_sum(sx, red);
   const float inv = 1.f / sqrtf(sx / static_cast<float>(dim) + eps);
   TO* orow = out + static_cast<size_t>(r) * dim;
-  for (int c = threadIdx.x; c < dim; c += blockDim.x) orow[c] = from_f<TO>(xr[c] * inv * (w[c] + o));
+  float* o32 = out32 ? out32 + static_cast<size_t>(r) * dim : nullptr;
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+    const float v = xr[c] * inv * (w[c] + o);
+    orow[c] = from_f<TO>(v);
+    if (o32) o32[c] = v;
+  }
 }
 
 // The same for dim % 4 == 0 and dim <= 4 * SN_MAXV * blockDim: 16-byte (fp32) / 8-byte (bf16) accesses, the row is read from global
@@ -141,8 +146,8 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
 
 template <typename TY, typename TO>
 __global__ void sandwich_norm_vec_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ wb, float ob,
-                                         const float* __restrict__ w, float o, TO* __restrict__ out, const int* __restrict__ rows, int dim,
-                                         float eps) {
+                                         const float* __restrict__ w, float o, TO* __restrict__ out, float* __restrict__ out32,
+                                         const int* __restrict__ rows, int dim, float eps) {
   __shared__ float red[33];
   const int r = blockIdx.x;
   float* xr = x + static_cast<size_t>(rows ? rows[r] : r) * dim;
@@ -196,7 +201,9 @@ __global__ void sandwich_norm_vec_kernel(float* __restrict__ x, const TY* __rest
     const int c = threadIdx.x + i * blockDim.x;
     if (c < nv) {
       const float4 g = load4(w + 4 * c);
-      store4(orow + 4 * c, make_float4(xv[i].x * inv * (g.x + o), xv[i].y * inv * (g.y + o), xv[i].z * inv * (g.z + o), xv[i].w * inv * (g.w + o)));
+      const float4 v = make_float4(xv[i].x * inv * (g.x + o), xv[i].y * inv * (g.y + o), xv[i].z * inv * (g.z + o), xv[i].w * inv * (g.w + o));
+      store4(orow + 4 * c, v);
+      if (out32) store4(out32 + static_cast<size_t>(r) * dim + 4 * c, v);
     }
   }
 }
@@ -671,23 +678,24 @@ DSB_EXPORT int dsb200_embed_sinusoid(const long long* ids, const void* table, in
 }
 
 // Per row of the fp32 residual x [n_rows, dim] (row rows[r] when `rows` is given): if y: x += rms_norm(y) * (wb + ob); if w:
-// out = rms_norm(x) * (w + o).  y and out are bf16 (dtype 0) or fp32 (dtype 1); the weights are fp32.
+// out = rms_norm(x) * (w + o).  y and out are bf16 (dtype 0) or fp32 (dtype 1); the weights are fp32.  out32 (optional, fp32
+// [n_rows, dim]) receives the normed values before their rounding to out's dtype (a router that decides in fp32 reads these).
 DSB_EXPORT int dsb200_sandwich_norm(float* x, const void* y, int y_dtype, const float* wb, float ob, const float* w, float o, void* out,
-                                    int out_dtype, const int* rows, int n_rows, int dim, float eps, cudaStream_t stream) {
+                                    int out_dtype, float* out32, const int* rows, int n_rows, int dim, float eps, cudaStream_t stream) {
   if (n_rows == 0) return DSB_OK;
   DSB_REQUIRE(y == nullptr || (wb != nullptr && rows == nullptr), "sandwich_norm: a branch needs its weight and cannot be combined with a row gather");
   DSB_REQUIRE(w == nullptr || out != nullptr, "sandwich_norm: an output norm needs an output");
   int block = dim >= 1024 ? 256 : 128;
   const bool vec = dim % 4 == 0 && dim <= 4 * SN_MAXV * 512 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(wb) |
-                                                                reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+                                                                reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(out32)) & 15) == 0;
   if (vec) {  // one 4-vector per thread and step, at most SN_MAXV steps
     block = 64;
     while (block * SN_MAXV * 4 < dim) block *= 2;
   }
 #define LAUNCH(TY, TO)                                                                                                              \
   do {                                                                                                                              \
-    if (vec) sandwich_norm_vec_kernel<TY, TO><<<n_rows, block, 0, stream>>>(x, (const TY*)y, wb, ob, w, o, (TO*)out, rows, dim, eps); \
-    else sandwich_norm_kernel<TY, TO><<<n_rows, block, 0, stream>>>(x, (const TY*)y, wb, ob, w, o, (TO*)out, rows, dim, eps);         \
+    if (vec) sandwich_norm_vec_kernel<TY, TO><<<n_rows, block, 0, stream>>>(x, (const TY*)y, wb, ob, w, o, (TO*)out, out32, rows, dim, eps); \
+    else sandwich_norm_kernel<TY, TO><<<n_rows, block, 0, stream>>>(x, (const TY*)y, wb, ob, w, o, (TO*)out, out32, rows, dim, eps);  \
   } while (0)
   if (y_dtype == 0 && out_dtype == 0) LAUNCH(bf16, bf16);
   else if (y_dtype == 0) LAUNCH(bf16, float);

@@ -227,7 +227,7 @@ def moe_gather(moe_out, scores, mapped_slots):
 # for any width in bf16 or fp32.  Device only: these ops have no host form (their oracles live with the tests).
 native.register_sigs({
     "dsb200_embed_sinusoid": "pp i pp p ii p",
-    "dsb200_sandwich_norm": "pp i p f p f p i p ii f p",
+    "dsb200_sandwich_norm": "pp i p f p f p i pp ii f p",
     "dsb200_latent_norm_append": "p i pp pp ppp iiii ii f i p",
     "dsb200_paged_flash_latent": "p i ll pp ppp iiiiii f ii p i p",
     "dsb200_gate_heads": "pp l p iii i p",
@@ -266,19 +266,23 @@ def embed_sinusoid(ids, table, tok_pos, freq):
     return out
 
 
-def sandwich_norm(x, y=None, wb=None, ob=0.0, w=None, o=0.0, eps=1e-6, out_dtype=torch.bfloat16, rows=None):
+def sandwich_norm(x, y=None, wb=None, ob=0.0, w=None, o=0.0, eps=1e-6, out_dtype=torch.bfloat16, rows=None, fp32_copy=False):
     """On the fp32 residual x [T, dim], in place: x += rms_norm(y) * (wb + ob) when a branch output y is given; returns
     rms_norm(x) * (w + o) in `out_dtype` when w is given (else None).  `rows` (int32 indices): normalise only those rows of x
-    (no branch then); the result has one row per index."""
+    (no branch then); the result has one row per index.  `fp32_copy`: also return the normed values before their rounding to
+    `out_dtype` -> (out, out_fp32); for an fp32 `out_dtype` both are the same tensor."""
     assert x.dtype == torch.float32 and x.is_contiguous() and x.is_cuda
     n = x.shape[0] if rows is None else rows.numel()
     out = torch.empty(n, x.shape[1], dtype=out_dtype, device=x.device) if w is not None else None
+    out32 = torch.empty(n, x.shape[1], dtype=torch.float32, device=x.device) if (fp32_copy and w is not None and out_dtype != torch.float32) else None
     if y is not None:
         assert y.shape == x.shape
         y = y if y.is_contiguous() else y.contiguous()  # a GEMM output whose rows were padded to the TMA stride (odd widths only)
     native.check(native.lib().dsb200_sandwich_norm(native.ptr(x), native.ptr(y), _dt(y) if y is not None else 0, native.ptr(wb), float(ob),
-                                                   native.ptr(w), float(o), native.ptr(out), _DT[out_dtype], native.ptr(rows), n, x.shape[1],
-                                                   float(eps), native.stream_ptr()))
+                                                   native.ptr(w), float(o), native.ptr(out), _DT[out_dtype], native.ptr(out32), native.ptr(rows), n,
+                                                   x.shape[1], float(eps), native.stream_ptr()))
+    if fp32_copy:
+        return out, (out32 if out32 is not None else out)
     return out
 
 

@@ -240,8 +240,9 @@ class LinasunInferenceModel(RaggedTransformer, DSInferenceModelBase):
             if self.moe_mods[li] is None:
                 _, h = self.norm_mod(x, y, nxt, branch_gamma=L["norm1b_w"])
             else:
-                _, h = self.norm_mod(x, y, L["norm2_w"], branch_gamma=L["norm1b_w"])
-                y = self.moe_mods[li](h, L["router_w"], L["experts_gu"], L["experts_dn"], correction=L["correction"])
+                # the router decides on the normed activations before their rounding (same pass, no separate conversion)
+                _, h, h32 = self.norm_mod(x, y, L["norm2_w"], branch_gamma=L["norm1b_w"], fp32_copy=True)
+                y = self.moe_mods[li](h, L["router_w"], L["experts_gu"], L["experts_dn"], correction=L["correction"], router_input=h32)
                 _, h = self.norm_mod(x, y, nxt, branch_gamma=L["norm2b_w"])
             if self._layer_hook is not None:
                 self._layer_hook(run, x)

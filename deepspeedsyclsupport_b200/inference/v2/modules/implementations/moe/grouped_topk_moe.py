@@ -61,11 +61,13 @@ class DSGroupedTopKMoE(DSMoEBase):
 
     def forward(self, hidden_states: torch.Tensor, gate_w: torch.Tensor, mlp_1_w: torch.Tensor, mlp_2_w: torch.Tensor,
                 mlp_1_b: Optional[torch.Tensor] = None, mlp_2_b: Optional[torch.Tensor] = None,
-                correction: Optional[torch.Tensor] = None) -> torch.Tensor:
+                correction: Optional[torch.Tensor] = None, router_input: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """`router_input`: fp32 [tokens, model_dim], the hidden states before their rounding to the activation dtype (the norm in front
+        can emit them in the same pass); without it the router reads the rounded hidden states."""
         c = self._config
         assert mlp_1_b is None and mlp_2_b is None, "these experts have no biases"
         assert (correction is not None) == c.use_correction
-        logits = dense_matmul(hidden_states.float(), gate_w)  # fp32 router logits from the (already rounded) activations
+        logits = dense_matmul(router_input if router_input is not None else hidden_states.float(), gate_w)  # fp32 router logits
         counts, scores, assignments, offsets = K.grouped_topk_gating(logits, c.top_k, correction, c.n_groups, c.keep_groups, c.normalize_scores)
         moe_in, cumsum, slots = K.moe_scatter_rows(hidden_states, counts, assignments, offsets)
         gu = self._grouped(moe_in, mlp_1_w, cumsum)

@@ -32,12 +32,15 @@ class DSSandwichRMSNorm(DSPreNormBase):
         return InferenceParameter.initialize(param.to(torch.float32).contiguous())
 
     def forward(self, residual: torch.Tensor, hidden_states: Optional[torch.Tensor], gamma: Optional[torch.Tensor],
-                beta: Optional[torch.Tensor] = None, branch_gamma: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+                beta: Optional[torch.Tensor] = None, branch_gamma: Optional[torch.Tensor] = None, fp32_copy: bool = False):
         """residual: fp32 stream (updated in place).  hidden_states: the finished sublayer's output or None; branch_gamma: the weight
         of the norm applied to it.  gamma: weight of the norm that feeds the next sublayer, None when nothing follows.
-        Returns (residual, normed input of the next sublayer or None)."""
+        Returns (residual, normed input of the next sublayer or None); with `fp32_copy` a third value: the same normed input before
+        its rounding to the activation dtype (what an fp32 router should decide on)."""
         c = self._config
         assert beta is None, "RMS norms have no shift"
         out = K.sandwich_norm(residual, hidden_states, branch_gamma, c.weight_offset, gamma, c.weight_offset, c.eps,
-                              out_dtype=DtypeEnum(c.output_dtype).value)
+                              out_dtype=DtypeEnum(c.output_dtype).value, fp32_copy=fp32_copy)
+        if fp32_copy:
+            return residual, out[0], out[1]
         return residual, out

@@ -372,9 +372,10 @@ int dsb200_fp8_rowwise_quantize(const void* x, void* q, float* scales, int rows,
 int dsb200_embed_sinusoid(const long long* ids, const void* table, int table_dtype, const int* tok_pos, const double* freq,
                           float* out, int n_tokens, int dim, dsb200_stream_t stream);
 /* Per row of the fp32 residual x [n_rows, dim] (row rows[r] when `rows` is given): if y: x += rms_norm(y) * (wb + ob); if w:
- * out = rms_norm(x) * (w + o).  y and out are bf16 (dtype 0) or fp32 (dtype 1); the weights are fp32. */
+ * out = rms_norm(x) * (w + o).  y and out are bf16 (dtype 0) or fp32 (dtype 1); the weights are fp32.  out32 (optional, fp32
+ * [n_rows, dim]) receives the normed values before their rounding to out's dtype (a router that decides in fp32 reads these). */
 int dsb200_sandwich_norm(float* x, const void* y, int y_dtype, const float* wb, float ob, const float* w, float o,
-                         void* out, int out_dtype, const int* rows, int n_rows, int dim, float eps,
+                         void* out, int out_dtype, float* out32, const int* rows, int n_rows, int dim, float eps,
                          dsb200_stream_t stream);
 /* lat [n_tokens, ld] holds (query latent [nq] | key/value latent [nkv]) of every token.  cq [n_tokens, nq] = plain-weight RMS norm
  * of the first part; the RMS-normed second part is written to the token's row of cache [blocks, block_size, cache_ld] (cache_ld >= nkv:

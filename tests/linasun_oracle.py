@@ -140,8 +140,11 @@ def make_config(width, vocab, layers, loop=None, eps=1e-5, softcap=20.0):
             "layers": layers, "loop": loop or {"start": 0, "stop": 0, "times": 1}}
 
 
-def random_weights(cfg, seed=0, dtype=torch.bfloat16):
-    """Weights in the checkpoint's naming, rounded to `dtype` (the oracle then uses the same rounded values)."""
+def random_weights(cfg, seed=0, dtype=torch.bfloat16, separated_router=False):
+    """Weights in the checkpoint's naming, rounded to `dtype` (the oracle then uses the same rounded values).
+    `separated_router`: the per-expert correction terms are a permutation of 0, 2, 4, ...: the selection then never hangs on a
+    close call (a 16-bit run of a random model otherwise picks another expert for a few tokens, and that spreads through attention),
+    while the combine weights stay the informative softmax scores."""
     g = torch.Generator().manual_seed(seed)
     D, V = cfg["width"], cfg["vocab"]
 
@@ -167,7 +170,7 @@ def random_weights(cfg, seed=0, dtype=torch.bfloat16):
             f = L["mlp"]
             E, ff = f["router"]["experts"], f["expert"]["ff"]
             W[p + "mlp.router"] = lin(E, D, 3.0)
-            W[p + "mlp.correction"] = small(E, 0.3)
+            W[p + "mlp.correction"] = (2.0 * torch.randperm(E, generator=g).float()).to(dtype) if separated_router else small(E, 0.3)
             for e in range(E):
                 W[p + f"mlp.e{e}.gate"], W[p + f"mlp.e{e}.up"], W[p + f"mlp.e{e}.down"] = lin(ff, D, 2.0), lin(ff, D, 2.0), lin(D, ff)
     return W

@@ -112,9 +112,11 @@ def test_sandwich_norm_modes(dt, dim):
     wb, w = (torch.randn(dim) * 0.3).cuda(), (torch.randn(dim) * 0.3).cuda()
     x1 = x0.double().cpu() + O.block_norm(y.cpu().double(), wb.cpu().double(), eps)
     x = x0.clone()
-    out = K.sandwich_norm(x, y, wb, 1.0, w, 1.0, eps, out_dtype=dt)
+    out, out32 = K.sandwich_norm(x, y, wb, 1.0, w, 1.0, eps, out_dtype=dt, fp32_copy=True)
     assert torch.allclose(x.cpu().double(), x1, rtol=1e-6, atol=1e-5)
     assert torch.allclose(out.cpu().double(), O.block_norm(x1, w.cpu().double(), eps), **_tol(dt))
+    assert out32.dtype == torch.float32 and torch.allclose(out32.cpu().double(), O.block_norm(x1, w.cpu().double(), eps), rtol=2e-5, atol=2e-5)
+    assert torch.equal(out32.to(dt), out)  # the unrounded copy rounds to the activation-dtype output
     x = x0.clone()  # branch only
     assert K.sandwich_norm(x, y, wb, 1.0, None, 0.0, eps) is None and torch.allclose(x.cpu().double(), x1, rtol=1e-6, atol=1e-5)
     x = x0.clone()  # norm only, plain weight, gathered rows
@@ -213,7 +215,7 @@ def test_tensor_core_latent_attention_finds_one_far_key():
 def test_bf16_model_on_the_cuda_core_attention_too(tmp_path_factory, monkeypatch):
     """bf16 normally takes the tensor-core attention; with it switched off the general kernel serves the same model."""
     monkeypatch.setenv("DSB200_LATENT_FLASH", "0")
-    cfg, w, path = _model("aligned", tmp_path_factory)
+    cfg, w, path = _model("aligned", tmp_path_factory, torch.bfloat16)
     eng = _engine(path, torch.bfloat16)
     assert not eng.model().attn_mods[0]._flash and eng.model().attn_mods[1].cache_rank == 96
     toks = _tokens(cfg, 40, 3)
@@ -339,12 +341,14 @@ CONFIGS = {
 _MODELS = {}
 
 
-def _model(name, tmp_path_factory):
-    if name not in _MODELS:
+def _model(name, tmp_path_factory, dt=torch.float32):
+    """fp32 runs get an informative router (every selection is compared tightly); bf16 runs get well separated selections."""
+    sep = dt == torch.bfloat16
+    if (name, sep) not in _MODELS:
         cfg = CONFIGS[name]
-        w = O.random_weights(cfg, seed=len(name))
-        _MODELS[name] = (cfg, w, O.write_model(str(tmp_path_factory.mktemp(name)), cfg, w))
-    return _MODELS[name]
+        w = O.random_weights(cfg, seed=len(name), separated_router=sep)
+        _MODELS[(name, sep)] = (cfg, w, O.write_model(str(tmp_path_factory.mktemp(name)), cfg, w))
+    return _MODELS[(name, sep)]
 
 
 def _engine(path, dt, pool_tokens=256, block=16, max_seqs=4):
@@ -357,15 +361,15 @@ def _engine(path, dt, pool_tokens=256, block=16, max_seqs=4):
 
 
 def _close(got, want, dt):
-    """Logit rows agree up to a per-row shift, relative to the spread of the logits.  fp32: every row, tightly.  bf16: rounding
-    can flip a close expert selection of a random router for single tokens, so the bound is on the median and the 90th percentile."""
+    """Every logit row agrees up to a per-row shift, relative to the spread of the logits.  fp32: tightly.  bf16: within what rounding
+    alone does to these random models (a plain pipeline with bf16-rounded matrix products lands at a median of ~0.02 and rows up to
+    ~0.09 of the spread), far below what a wrong key, a lost page or a wrong expert would cause (order 1)."""
     d = got.cpu().double() - want
     d = d - d.mean(-1, keepdim=True)
     err = d.pow(2).mean(-1).sqrt() / want.std()
     if dt == torch.float32:
         return float(err.max()) < 2e-5, float(err.max())
-    q = torch.quantile(err, torch.tensor([0.5, 0.9], dtype=err.dtype))
-    return float(q[0]) < 2.5e-2 and float(q[1]) < 8e-2, q.tolist()
+    return float(err.max()) < 0.15 and float(err.median()) < 0.04, (float(err.median()), float(err.max()))
 
 
 def _tokens(cfg, n, seed):
@@ -376,7 +380,7 @@ def _tokens(cfg, n, seed):
 @pytest.mark.parametrize("dt", DTYPES)
 @pytest.mark.parametrize("name", list(CONFIGS))
 def test_whole_prompt_and_every_layer(name, dt, tmp_path_factory):
-    cfg, w, path = _model(name, tmp_path_factory)
+    cfg, w, path = _model(name, tmp_path_factory, dt)
     eng = _engine(path, dt)
     toks = _tokens(cfg, 45, 1)
     res, got_res = [], []
@@ -388,8 +392,8 @@ def test_whole_prompt_and_every_layer(name, dt, tmp_path_factory):
         if dt == torch.float32:
             assert torch.allclose(a.cpu().double(), b, rtol=1e-4, atol=1e-4), f"layer run {r}"
         else:
-            row = (a.cpu().double() - b).norm(dim=-1) / b.norm(dim=-1)  # a flipped close expert selection spoils single rows only
-            assert float(row.median()) < 2e-2, f"layer run {r}"
+            row = (a.cpu().double() - b).norm(dim=-1) / b.norm(dim=-1)
+            assert float(row.max()) < 0.15 and float(row.median()) < 0.03, f"layer run {r}"
     ok, err = _close(got, want, dt)
     assert ok, err
     assert got[0].isfinite().all()  # the first token attends to itself only
@@ -400,7 +404,7 @@ def test_whole_prompt_and_every_layer(name, dt, tmp_path_factory):
 @pytest.mark.parametrize("name,cuts", [("odd", [1] * 40), ("odd", [2, 2, 15, 1, 17, 3]), ("aligned", [16, 16, 1, 1, 6]), ("aligned", [31, 2, 7]), ("looped", [3, 33, 2, 2])])
 def test_portions_and_token_by_token_equal_the_whole_prompt(name, cuts, dt, tmp_path_factory):
     """Prefill against decoding token by token, and portions cut inside pages (block 16) down to two tokens."""
-    cfg, w, path = _model(name, tmp_path_factory)
+    cfg, w, path = _model(name, tmp_path_factory, dt)
     eng = _engine(path, dt)
     toks = _tokens(cfg, sum(cuts), 2)
     want = O.forward(cfg, w, toks.tolist())
@@ -417,7 +421,7 @@ def test_portions_and_token_by_token_equal_the_whole_prompt(name, cuts, dt, tmp_
 def test_unequal_requests_in_one_batch_and_reused_pages(dt, tmp_path_factory):
     """Four requests of unequal length share steps (portions beside single tokens), finish at different times, and two more
     take over their sequence slots and pages: every logit row equals the request run alone."""
-    cfg, w, path = _model("odd", tmp_path_factory)
+    cfg, w, path = _model("odd", tmp_path_factory, dt)
     eng = _engine(path, dt, pool_tokens=160, block=16)
     prompts = {u: _tokens(cfg, n, 10 + u) for u, n in ((0, 50), (1, 17), (2, 33), (3, 1), (4, 48), (5, 31))}
     want = {u: O.forward(cfg, w, p.tolist()) for u, p in prompts.items()}
