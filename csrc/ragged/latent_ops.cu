@@ -74,6 +74,10 @@ __global__ void embed_sinusoid_kernel(const long long* __restrict__ ids, const T
   const double p = static_cast<double>(tok_pos[t]);
   const TW* row = table + id * dim;
   float* o = out + static_cast<size_t>(t) * dim;
+  if (freq == nullptr) {  // no position vector: the table row alone starts the stream
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = to_f(row[i]);
+    return;
+  }
   for (int i = threadIdx.x; 2 * i < dim; i += blockDim.x) {
     double s, c;
     sincos(p * freq[i], &s, &c);
@@ -84,12 +88,13 @@ __global__ void embed_sinusoid_kernel(const long long* __restrict__ ids, const T
 
 // --------------------------------------------------------------------------------------------------------------------- norms
 // Row r of the fp32 residual (row rows[r] when `rows` is given; then nothing is written back to x):
-//   y given:   x <- x + y / sqrt(mean(y^2) + eps) * (wb + ob)
+//   y given:   x <- x + ym * y / sqrt(mean(y^2) + eps) * (wb + ob)
 //   w given:   out <- x / sqrt(mean(x^2) + eps) * (w + o)      (and the same values unrounded into out32 when that is given)
+//   plain:     out <- x                                        (the stream itself in out's dtype: blocks whose sublayers read it unnormed)
 template <typename TY, typename TO>
-__global__ void sandwich_norm_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ wb, float ob,
+__global__ void sandwich_norm_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ wb, float ob, float ym,
                                      const float* __restrict__ w, float o, TO* __restrict__ out, float* __restrict__ out32,
-                                     const int* __restrict__ rows, int dim, float eps) {
+                                     const int* __restrict__ rows, int dim, float eps, int plain) {
   __shared__ float red[33];
   const int r = blockIdx.x;
   float* xr = x + static_cast<size_t>(rows ? rows[r] : r) * dim;
@@ -102,7 +107,7 @@ __global__ void sandwich_norm_kernel(float* __restrict__ x, const TY* __restrict
       sy += v * v;
     }
     sy = block_sum(sy, red);
-    const float inv = 1.f / sqrtf(sy / static_cast<float>(dim) + eps);
+    const float inv = ym / sqrtf(sy / static_cast<float>(dim) + eps);
     for (int c = threadIdx.x; c < dim; c += blockDim.x) {
       const float v = xr[c] + to_f(yr[c]) * inv * (wb[c] + ob);
       xr[c] = v;  // read back below by this same thread only
@@ -113,6 +118,11 @@ __global__ void sandwich_norm_kernel(float* __restrict__ x, const TY* __restrict
       const float v = xr[c];
       sx += v * v;
     }
+  }
+  if (plain) {
+    TO* orow = out + static_cast<size_t>(r) * dim;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) orow[c] = from_f<TO>(xr[c]);
+    return;
   }
   if (w == nullptr) return;
   sx = block_sum(sx, red);
@@ -145,9 +155,9 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
 }
 
 template <typename TY, typename TO>
-__global__ void sandwich_norm_vec_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ wb, float ob,
+__global__ void sandwich_norm_vec_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ wb, float ob, float ym,
                                          const float* __restrict__ w, float o, TO* __restrict__ out, float* __restrict__ out32,
-                                         const int* __restrict__ rows, int dim, float eps) {
+                                         const int* __restrict__ rows, int dim, float eps, int plain) {
   __shared__ float red[33];
   const int r = blockIdx.x;
   float* xr = x + static_cast<size_t>(rows ? rows[r] : r) * dim;
@@ -168,7 +178,7 @@ __global__ void sandwich_norm_vec_kernel(float* __restrict__ x, const TY* __rest
       }
     }
     sy = block_sum(sy, red);
-    const float inv = 1.f / sqrtf(sy / static_cast<float>(dim) + eps);
+    const float inv = ym / sqrtf(sy / static_cast<float>(dim) + eps);
 #pragma unroll
     for (int i = 0; i < SN_MAXV; ++i) {
       const int c = threadIdx.x + i * blockDim.x;
@@ -182,7 +192,7 @@ __global__ void sandwich_norm_vec_kernel(float* __restrict__ x, const TY* __rest
         sx += xv[i].x * xv[i].x + xv[i].y * xv[i].y + xv[i].z * xv[i].z + xv[i].w * xv[i].w;
       }
     }
-  } else if (w != nullptr) {
+  } else if (w != nullptr || plain) {
 #pragma unroll
     for (int i = 0; i < SN_MAXV; ++i) {
       const int c = threadIdx.x + i * blockDim.x;
@@ -192,10 +202,18 @@ __global__ void sandwich_norm_vec_kernel(float* __restrict__ x, const TY* __rest
       }
     }
   }
+  TO* orow = out + static_cast<size_t>(r) * dim;
+  if (plain) {
+#pragma unroll
+    for (int i = 0; i < SN_MAXV; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < nv) store4(orow + 4 * c, xv[i]);
+    }
+    return;
+  }
   if (w == nullptr) return;
   sx = block_sum(sx, red);
   const float inv = 1.f / sqrtf(sx / static_cast<float>(dim) + eps);
-  TO* orow = out + static_cast<size_t>(r) * dim;
 #pragma unroll
   for (int i = 0; i < SN_MAXV; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
@@ -468,7 +486,7 @@ __global__ void softcap_kernel(float* __restrict__ x, long long ld, int cols, lo
 // One warp per token.  Shared memory per warp: E selection scores + G group scores.  Ties go to the lower index.
 __global__ void grouped_topk_gating_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int* __restrict__ expert_counts,
                                            float* __restrict__ scores, int* __restrict__ assignments, int* __restrict__ offsets, int n_tokens,
-                                           int E, int K, int G, int keep, int normalize) {
+                                           int E, int K, int G, int keep, int normalize, int sigmoid_scores) {
   extern __shared__ float smem[];
   const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tok = blockIdx.x * (blockDim.x >> 5) + wib;
@@ -476,14 +494,19 @@ __global__ void grouped_topk_gating_kernel(const float* __restrict__ logits, con
   float* choice = smem + static_cast<size_t>(wib) * (E + G);
   float* gsc = choice + E;
   const float* lg = logits + static_cast<size_t>(tok) * E;
-  float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) sum += expf(lg[e] - mx);
-  sum = warp_sum(sum);
-  const float inv = 1.f / sum;
-  for (int e = lane; e < E; e += 32) choice[e] = expf(lg[e] - mx) * inv + (correction ? correction[e] : 0.f);
+  float mx = 0.f, inv = 1.f;
+  if (!sigmoid_scores) {
+    mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += expf(lg[e] - mx);
+    sum = warp_sum(sum);
+    inv = 1.f / sum;
+  }
+  // score of expert e: its softmax probability, or (sigmoid_scores) 1 / (1 + exp(-logit)) on its own
+  for (int e = lane; e < E; e += 32)
+    choice[e] = (sigmoid_scores ? 1.f / (1.f + expf(-lg[e])) : expf(lg[e] - mx) * inv) + (correction ? correction[e] : 0.f);
   __syncwarp();
   if (G > 1 && keep < G) {
     const int per = E / G;
@@ -523,7 +546,7 @@ __global__ void grouped_topk_gating_kernel(const float* __restrict__ logits, con
     }
     float s = 0.f;
     if (best_e >= 0) {
-      s = expf(lg[best_e] - mx) * inv;
+      s = sigmoid_scores ? 1.f / (1.f + expf(-lg[best_e])) : expf(lg[best_e] - mx) * inv;
       if (lane == 0) choice[best_e] = -INFINITY;
     }
     __syncwarp();
@@ -547,16 +570,23 @@ __global__ void expert_cumsum_kernel(const int* __restrict__ counts, long long* 
 
 template <typename T, bool VEC>
 __global__ void moe_scatter_kernel(const T* __restrict__ x, const int* __restrict__ assignments, const int* __restrict__ offsets,
-                                   const long long* __restrict__ cumsum, T* __restrict__ moe_in, int* __restrict__ mapped_slots, int dim, int K) {
+                                   const long long* __restrict__ cumsum, T* __restrict__ moe_in, int* __restrict__ mapped_slots, int dim, int K,
+                                   const float* __restrict__ row_scale) {
   const int t = blockIdx.x;
   for (int k = 0; k < K; ++k) {
     const int e = assignments[t * K + k];
     const long long slot = (e == 0 ? 0 : cumsum[e - 1]) + offsets[t * K + k];
     if (threadIdx.x == 0) mapped_slots[t * K + k] = static_cast<int>(slot);
+    const float sc = row_scale ? row_scale[t * K + k] : 1.f;  // experts that weigh their input: the copy is scaled (in fp32, then rounded)
     if constexpr (VEC) {
-      for (int c = threadIdx.x * 4; c < dim; c += blockDim.x * 4) store4(moe_in + slot * dim + c, load4(x + static_cast<size_t>(t) * dim + c));
+      for (int c = threadIdx.x * 4; c < dim; c += blockDim.x * 4) {
+        float4 v = load4(x + static_cast<size_t>(t) * dim + c);
+        if (row_scale) v = make_float4(v.x * sc, v.y * sc, v.z * sc, v.w * sc);
+        store4(moe_in + slot * dim + c, v);
+      }
     } else {
-      for (int c = threadIdx.x; c < dim; c += blockDim.x) moe_in[slot * dim + c] = x[static_cast<size_t>(t) * dim + c];
+      for (int c = threadIdx.x; c < dim; c += blockDim.x)
+        moe_in[slot * dim + c] = row_scale ? from_f<T>(to_f(x[static_cast<size_t>(t) * dim + c]) * sc) : x[static_cast<size_t>(t) * dim + c];
     }
   }
 }
@@ -569,7 +599,7 @@ __global__ void moe_gather_kernel(const T* __restrict__ moe_out, const float* __
     for (int c = threadIdx.x * 4; c < dim; c += blockDim.x * 4) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int k = 0; k < K; ++k) {
-        const float s = scores[t * K + k];
+        const float s = scores ? scores[t * K + k] : 1.f;
         const float4 v = load4(moe_out + static_cast<size_t>(mapped_slots[t * K + k]) * dim + c);
         acc.x = fmaf(s, v.x, acc.x); acc.y = fmaf(s, v.y, acc.y); acc.z = fmaf(s, v.z, acc.z); acc.w = fmaf(s, v.w, acc.w);
       }
@@ -578,7 +608,8 @@ __global__ void moe_gather_kernel(const T* __restrict__ moe_out, const float* __
   } else {
     for (int c = threadIdx.x; c < dim; c += blockDim.x) {
       float acc = 0.f;
-      for (int k = 0; k < K; ++k) acc = fmaf(scores[t * K + k], to_f(moe_out[static_cast<size_t>(mapped_slots[t * K + k]) * dim + c]), acc);
+      for (int k = 0; k < K; ++k)
+        acc = fmaf(scores ? scores[t * K + k] : 1.f, to_f(moe_out[static_cast<size_t>(mapped_slots[t * K + k]) * dim + c]), acc);
       out[static_cast<size_t>(t) * dim + c] = acc;
     }
   }
@@ -665,7 +696,8 @@ static inline int grid_for(long long n, int block) {
 }
 
 // out[t, :] = table[ids[t], :] + sinusoid(tok_pos[t]): entry 2i = sin(p f_i), entry 2i + 1 = cos(p f_i); `freq` holds the
-// ceil(dim / 2) frequencies as doubles on the device.  table_dtype: 0 = bf16, 1 = fp32.  out is fp32.
+// ceil(dim / 2) frequencies as doubles on the device, or is null for no position vector (tok_pos is then unused).
+// table_dtype: 0 = bf16, 1 = fp32.  out is fp32.
 DSB_EXPORT int dsb200_embed_sinusoid(const long long* ids, const void* table, int table_dtype, const int* tok_pos, const double* freq,
                                      float* out, int n_tokens, int dim, cudaStream_t stream) {
   if (n_tokens == 0) return DSB_OK;
@@ -677,14 +709,17 @@ DSB_EXPORT int dsb200_embed_sinusoid(const long long* ids, const void* table, in
   return DSB_OK;
 }
 
-// Per row of the fp32 residual x [n_rows, dim] (row rows[r] when `rows` is given): if y: x += rms_norm(y) * (wb + ob); if w:
-// out = rms_norm(x) * (w + o).  y and out are bf16 (dtype 0) or fp32 (dtype 1); the weights are fp32.  out32 (optional, fp32
-// [n_rows, dim]) receives the normed values before their rounding to out's dtype (a router that decides in fp32 reads these).
-DSB_EXPORT int dsb200_sandwich_norm(float* x, const void* y, int y_dtype, const float* wb, float ob, const float* w, float o, void* out,
-                                    int out_dtype, float* out32, const int* rows, int n_rows, int dim, float eps, cudaStream_t stream) {
+// Per row of the fp32 residual x [n_rows, dim] (row rows[r] when `rows` is given): if y: x += y_mult * rms_norm(y) * (wb + ob); if w:
+// out = rms_norm(x) * (w + o); if plain_out (and no w): out = x.  y and out are bf16 (dtype 0) or fp32 (dtype 1); the weights are fp32.
+// out32 (optional, fp32 [n_rows, dim]) receives the normed values before their rounding to out's dtype (a router that decides in fp32
+// reads these).
+DSB_EXPORT int dsb200_sandwich_norm(float* x, const void* y, int y_dtype, const float* wb, float ob, float y_mult, const float* w, float o,
+                                    void* out, int out_dtype, float* out32, const int* rows, int n_rows, int dim, float eps, int plain_out,
+                                    cudaStream_t stream) {
   if (n_rows == 0) return DSB_OK;
   DSB_REQUIRE(y == nullptr || (wb != nullptr && rows == nullptr), "sandwich_norm: a branch needs its weight and cannot be combined with a row gather");
   DSB_REQUIRE(w == nullptr || out != nullptr, "sandwich_norm: an output norm needs an output");
+  DSB_REQUIRE(!plain_out || (w == nullptr && out != nullptr && out32 == nullptr), "sandwich_norm: the plain output replaces the output norm");
   int block = dim >= 1024 ? 256 : 128;
   const bool vec = dim % 4 == 0 && dim <= 4 * SN_MAXV * 512 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(wb) |
                                                                 reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(out32)) & 15) == 0;
@@ -694,8 +729,8 @@ DSB_EXPORT int dsb200_sandwich_norm(float* x, const void* y, int y_dtype, const 
   }
 #define LAUNCH(TY, TO)                                                                                                              \
   do {                                                                                                                              \
-    if (vec) sandwich_norm_vec_kernel<TY, TO><<<n_rows, block, 0, stream>>>(x, (const TY*)y, wb, ob, w, o, (TO*)out, out32, rows, dim, eps); \
-    else sandwich_norm_kernel<TY, TO><<<n_rows, block, 0, stream>>>(x, (const TY*)y, wb, ob, w, o, (TO*)out, out32, rows, dim, eps);  \
+    if (vec) sandwich_norm_vec_kernel<TY, TO><<<n_rows, block, 0, stream>>>(x, (const TY*)y, wb, ob, y_mult, w, o, (TO*)out, out32, rows, dim, eps, plain_out); \
+    else sandwich_norm_kernel<TY, TO><<<n_rows, block, 0, stream>>>(x, (const TY*)y, wb, ob, y_mult, w, o, (TO*)out, out32, rows, dim, eps, plain_out);  \
   } while (0)
   if (y_dtype == 0 && out_dtype == 0) LAUNCH(bf16, bf16);
   else if (y_dtype == 0) LAUNCH(bf16, float);
@@ -836,13 +871,14 @@ DSB_EXPORT int dsb200_softcap(float* x, long long ld, long long rows, int cols, 
   return DSB_OK;
 }
 
-// Router: softmax over the E logits of a token; selection score = score + correction[e] (correction may be null); experts are split
+// Router: scores = softmax over the E logits of a token, or (sigmoid_scores) the sigmoid of every logit on its own; selection score =
+// score + correction[e] (correction may be null); experts are split
 // into `groups` contiguous groups of equal size, of which the `keep` with the largest maximal selection score stay selectable; the top_k
 // selectable experts by selection score are assigned; their weights are the uncorrected scores (divided by their sum when
 // `normalize`).  Outputs as dsb200_top_k_gating; expert_counts must be zeroed by the caller.
 DSB_EXPORT int dsb200_grouped_topk_gating(const float* logits, const float* correction, int* expert_counts, float* scores, int* assignments,
                                           int* offsets, int n_tokens, int n_experts, int top_k, int groups, int keep, int normalize,
-                                          cudaStream_t stream) {
+                                          int sigmoid_scores, cudaStream_t stream) {
   if (n_tokens == 0) return DSB_OK;
   DSB_REQUIRE(top_k >= 1 && top_k <= 32 && top_k <= n_experts && n_experts <= 2048, "grouped_topk_gating: k=%d (1..32), experts=%d (<=2048)",
               top_k, n_experts);
@@ -851,20 +887,21 @@ DSB_EXPORT int dsb200_grouped_topk_gating(const float* logits, const float* corr
   const int wpb = 4;
   const size_t smem = static_cast<size_t>(wpb) * (n_experts + groups) * sizeof(float);
   grouped_topk_gating_kernel<<<(n_tokens + wpb - 1) / wpb, wpb * 32, smem, stream>>>(logits, correction, expert_counts, scores, assignments,
-                                                                                   offsets, n_tokens, n_experts, top_k, groups, keep, normalize);
+                                                                                   offsets, n_tokens, n_experts, top_k, groups, keep, normalize, sigmoid_scores);
   DSB_CHECK_CUDA(cudaGetLastError());
   return DSB_OK;
 }
 
 // Rows of x [n_tokens, dim] copied into expert-sorted order (any dim; dtype 0 = bf16, 1 = fp32); also writes the inclusive
-// per-expert row cumsum and every (token, k)'s row.
+// per-expert row cumsum and every (token, k)'s row.  row_scale (optional, fp32 [n_tokens, top_k]): copy k of token t is multiplied by
+// row_scale[t, k] (routers whose weight applies to the expert's input).
 DSB_EXPORT int dsb200_moe_scatter_rows(const void* x, const int* expert_counts, const int* assignments, const int* offsets,
                                        long long* expert_cumsum, void* moe_in, int* mapped_slots, int n_tokens, int n_experts, int dim,
-                                       int top_k, int dtype, cudaStream_t stream) {
+                                       int top_k, int dtype, const float* row_scale, cudaStream_t stream) {
   if (n_tokens == 0) return DSB_OK;
   expert_cumsum_kernel<<<1, 32, 0, stream>>>(expert_counts, expert_cumsum, n_experts);
   const bool vec = dim % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(moe_in)) & 15) == 0;
-#define LAUNCH(T, V) moe_scatter_kernel<T, V><<<n_tokens, 256, 0, stream>>>((const T*)x, assignments, offsets, expert_cumsum, (T*)moe_in, mapped_slots, dim, top_k)
+#define LAUNCH(T, V) moe_scatter_kernel<T, V><<<n_tokens, 256, 0, stream>>>((const T*)x, assignments, offsets, expert_cumsum, (T*)moe_in, mapped_slots, dim, top_k, row_scale)
   if (dtype == 0 && vec) LAUNCH(bf16, true);
   else if (dtype == 0) LAUNCH(bf16, false);
   else if (vec) LAUNCH(float, true);
@@ -874,7 +911,7 @@ DSB_EXPORT int dsb200_moe_scatter_rows(const void* x, const int* expert_counts, 
   return DSB_OK;
 }
 
-// out[t, :] (fp32) = sum_k scores[t, k] * moe_out[mapped_slots[t, k], :]
+// out[t, :] (fp32) = sum_k scores[t, k] * moe_out[mapped_slots[t, k], :]; scores may be null (plain sum)
 DSB_EXPORT int dsb200_moe_gather_rows(const void* moe_out, const float* scores, const int* mapped_slots, float* out, int n_tokens, int dim,
                                       int top_k, int dtype, cudaStream_t stream) {
   if (n_tokens == 0) return DSB_OK;

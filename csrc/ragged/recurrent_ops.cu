@@ -1,0 +1,684 @@
+// build: precise-math
+// Ragged-batch kernels for decoders whose token mixers carry per-sequence state besides (or instead of) a paged key/value cache:
+// short causal convolutions over time, sliding-window attention that keeps the first tokens of a sequence visible, and two
+// recurrent matrix memories.  Every kernel takes its sizes as arguments and exists for 16-bit (bf16) and 32-bit activations;
+// recurrent state, gates, decays, norms and softmax are always fp32.
+//
+// A batch is described per sequence by `seq_desc` (int4: first row of the sequence in the batch, number of new tokens, tokens
+// seen before this step = position of the first new token, state slot).  State of a sequence lives in its slot of per-layer
+// buffers; a sequence whose first new token has position 0 starts from zero state whatever its slot holds (slots are reused
+// without being cleared).
+//
+//   window_qk_prepare     short convolution of the query / key projections -> values (= convolved keys) into cache plane 1,
+//                         RMS norm over the whole query / key projection, interleaved rotary on the first rot_dims of every head,
+//                         keys into cache plane 0
+//   conv_state_update     keeps the last taps - 1 projected rows of every sequence for the next step
+//   window_attention      softmax attention over the paged cache; query i sees key j <= i when i - j < window or j < keep_first
+//   matrix_memory_scan    S <- a S + b k v^T, n <- a n + b k with log-space gates and a running maximum that starts at 0;
+//                         o = S^T q / (max(|n . q|, exp(-m)) + 1e-6)
+//   delta_prepare         short convolution + silu of q / k / v projections, unit-length q and k per head
+//   delta_rule_scan       S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, one decay per head and key channel
+//   head_norm_gate        per-head RMS norm of the fp32 read-out, times a weight, times sigmoid(gate), times a constant
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "../common/host.h"
+
+namespace dsb {
+namespace recur {
+
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// reductions over the block; every thread gets the result.  `red` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float siluf_(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float logsigmoidf_(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+// ------------------------------------------------------------------------------------------------------ short convolutions
+// Value of channel c of the convolution at token i of a sequence's new tokens: sum_j w[c, j] * u(i - (taps - 1) + j), where u(ii) is
+// row ii of the new tokens for ii >= 0, the kept row taps - 1 + ii of the sequence's state for ii < 0 when that position exists
+// (seen + ii >= 0), and zero before the sequence's start.  `u` points at the channel in the sequence's first new row (row stride
+// ld), `st` at the channel in row 0 of the kept rows (row stride st_ld).
+template <typename T>
+__device__ __forceinline__ float conv_at(const T* __restrict__ u, long long ld, const T* __restrict__ st, int st_ld,
+                                         const float* __restrict__ w, int taps, int i, int seen) {
+  float acc = 0.f;
+  for (int j = 0; j < taps; ++j) {
+    const int ii = i - (taps - 1) + j;
+    float v = 0.f;
+    if (ii >= 0) v = to_f(u[static_cast<long long>(ii) * ld]);
+    else if (seen + ii >= 0) v = to_f(st[(taps - 1 + ii) * st_ld]);
+    acc = fmaf(w[j], v, acc);
+  }
+  return acc;
+}
+
+// state [slots, taps - 1, st_ld], columns st_col0 .. st_col0 + C: after the step, row j holds the projected values of position
+// seen + n - (taps - 1) + j.
+template <typename T>
+__global__ void conv_state_update_kernel(const T* __restrict__ proj, long long ld, int col0, T* __restrict__ state, int st_ld, int st_col0,
+                                         const int4* __restrict__ seq_desc, int C, int taps) {
+  const int4 sd = seq_desc[blockIdx.y];
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  T* st = state + (static_cast<size_t>(sd.w) * (taps - 1)) * st_ld + st_col0 + c;
+  const T* u = proj + static_cast<long long>(sd.x) * ld + col0 + c;
+  for (int j = 0; j < taps - 1; ++j) {  // ascending: row j is rewritten after the only read of it (rows j + n are read, n >= 1)
+    const int ii = sd.y - (taps - 1) + j;  // index among the new tokens of the position row j will hold
+    if (ii >= 0) st[j * st_ld] = u[static_cast<long long>(ii) * ld];
+    else if (sd.z + ii >= 0) st[j * st_ld] = st[(j + sd.y) * st_ld];
+  }
+}
+
+// One block per token.  proj row = (... | q projection [H d] at q_col0 | k projection [G d] at k_col0 | ...).  Shared memory: (H + G) d
+// convolved values + rot_dims sines / cosines.
+template <typename T>
+__global__ void window_qk_prepare_kernel(const T* __restrict__ proj, long long ld, int q_col0, int k_col0, const float* __restrict__ conv_q,
+                                         const float* __restrict__ conv_k, const float* __restrict__ norm_q, const float* __restrict__ norm_k,
+                                         const T* __restrict__ state, const int4* __restrict__ seq_desc, const int* __restrict__ tok_seq,
+                                         const int* __restrict__ tok_pos, const int* __restrict__ block_table, int bt_stride, int block_size,
+                                         T* __restrict__ cache, T* __restrict__ q_out, long long q_ld, const double* __restrict__ freq, int H,
+                                         int G, int d, int taps, int rot_dims, float eps) {
+  extern __shared__ float sm[];
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const int nq = H * d, nk = G * d, C = nq + nk;
+  float* y = sm;            // [C]: q channels then k channels
+  float* cs = sm + C;       // [rot_dims / 2] cosines, then sines
+  float* sn = cs + rot_dims / 2;
+  const int seq = tok_seq[t], pos = tok_pos[t];
+  const int4 sd = seq_desc[seq];
+  const int i = t - sd.x;  // index among the sequence's new tokens
+  const T* st = state + static_cast<size_t>(sd.w) * (taps - 1) * C;
+  const T* u0 = proj + static_cast<long long>(sd.x) * ld;
+  const int blk = block_table[static_cast<size_t>(seq) * bt_stride + pos / block_size];
+  T* krow = cache + ((static_cast<size_t>(blk) * 2 + 0) * block_size + pos % block_size) * nk;
+  T* vrow = cache + ((static_cast<size_t>(blk) * 2 + 1) * block_size + pos % block_size) * nk;
+  float sq = 0.f, sk = 0.f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const bool is_q = c < nq;
+    const int cc = is_q ? c : c - nq;
+    const float v = conv_at(u0 + (is_q ? q_col0 : k_col0) + cc, ld, st + c, C, (is_q ? conv_q : conv_k) + static_cast<size_t>(cc) * taps, taps, i,
+                            sd.z);
+    y[c] = v;
+    if (is_q) sq += v * v;
+    else {
+      sk += v * v;
+      vrow[cc] = from_f<T>(v);  // the values are the keys as they leave the convolution
+    }
+  }
+  for (int f = threadIdx.x; f < rot_dims / 2; f += blockDim.x) {
+    double s, c;
+    sincos(static_cast<double>(pos) * freq[f], &s, &c);
+    cs[f] = static_cast<float>(c);
+    sn[f] = static_cast<float>(s);
+  }
+  sq = block_sum(sq, red);
+  sk = block_sum(sk, red);  // (the barriers inside also publish y, cs, sn)
+  const float inv_q = 1.f / sqrtf(sq / static_cast<float>(nq) + eps), inv_k = 1.f / sqrtf(sk / static_cast<float>(nk) + eps);
+  T* qrow = q_out + static_cast<long long>(t) * q_ld;
+  for (int pr = threadIdx.x; pr < C / 2; pr += blockDim.x) {
+    const int c = 2 * pr;
+    const bool is_q = c < nq;
+    const int cc = is_q ? c : c - nq;
+    const float inv = is_q ? inv_q : inv_k;
+    const float* nw = is_q ? norm_q : norm_k;
+    float a = y[c] * inv * nw[cc], b = y[c + 1] * inv * nw[cc + 1];
+    const int within = cc % d;
+    if (within < rot_dims) {
+      const float co = cs[within >> 1], si = sn[within >> 1];
+      const float ra = a * co - b * si, rb = b * co + a * si;
+      a = ra;
+      b = rb;
+    }
+    T* dst = is_q ? qrow : krow;
+    dst[cc] = from_f<T>(a);
+    dst[cc + 1] = from_f<T>(b);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------- sliding-window attention
+// One block per (token, query head).  Visible keys of a query at position p: [0, min(keep, p + 1)) and [max(p - window + 1, that), p].
+// They are walked in chunks of WA_CHUNK with a running maximum / sum (fp32).  cache [blocks, 2, block_size, G, d]: plane 0 keys, 1 values.
+constexpr int WA_CHUNK = 256, WA_THREADS = 128;
+template <typename T>
+__global__ void __launch_bounds__(WA_THREADS)
+window_attention_kernel(const T* __restrict__ q, long long q_ld, const T* __restrict__ cache, const int* __restrict__ tok_seq,
+                        const int* __restrict__ tok_pos, const int* __restrict__ block_table, int bt_stride, int block_size, T* __restrict__ out,
+                        long long out_ld, int H, int G, int d, int window, int keep, float scale, float out_scale) {
+  extern __shared__ float sm[];
+  __shared__ float red[33];
+  __shared__ float sc[WA_CHUNK];
+  __shared__ int key_row[WA_CHUNK];  // row of the key in the cache: block * 2 * block_size + slot (plane 0)
+  const int t = blockIdx.x, h = blockIdx.y, g = h / (H / G);
+  const int seq = tok_seq[t], pos = tok_pos[t];
+  float* qs = sm;  // [d]
+  float* acc = sm + d;  // [d]
+  for (int c = threadIdx.x; c < d; c += WA_THREADS) {
+    qs[c] = to_f(q[static_cast<long long>(t) * q_ld + h * d + c]) * scale;
+    acc[c] = 0.f;
+  }
+  const int kept = min(keep, pos + 1);
+  const int b0 = max(max(0, pos - window + 1), kept);
+  const int n = kept + (pos - b0 + 1);
+  const int* bt = block_table + static_cast<size_t>(seq) * bt_stride;
+  const size_t row_elems = static_cast<size_t>(G) * d, plane = static_cast<size_t>(block_size) * row_elems;
+  float m_run = -INFINITY, l_run = 0.f;
+  __syncthreads();
+  for (int x0 = 0; x0 < n; x0 += WA_CHUNK) {
+    const int cn = min(WA_CHUNK, n - x0);
+    float mx = -INFINITY;
+    for (int x = threadIdx.x; x < cn; x += WA_THREADS) {
+      const int j = (x0 + x) < kept ? (x0 + x) : b0 + (x0 + x - kept);
+      const int row = bt[j / block_size] * 2 * block_size + j % block_size;
+      key_row[x] = row;
+      const T* kr = cache + static_cast<size_t>(row) * row_elems + g * d;
+      float s = 0.f;
+      for (int c = 0; c < d; ++c) s = fmaf(qs[c], to_f(kr[c]), s);
+      sc[x] = s;
+      mx = fmaxf(mx, s);
+    }
+    mx = block_max(mx, red);
+    const float m_new = fmaxf(m_run, mx);
+    float ls = 0.f;
+    for (int x = threadIdx.x; x < cn; x += WA_THREADS) {
+      const float p = expf(sc[x] - m_new);
+      sc[x] = p;
+      ls += p;
+    }
+    ls = block_sum(ls, red);
+    const float corr = expf(m_run - m_new);  // 0 for the first chunk (m_run = -inf)
+    l_run = l_run * corr + ls;
+    m_run = m_new;
+    for (int c = threadIdx.x; c < d; c += WA_THREADS) {
+      float a = acc[c] * corr;
+      for (int x = 0; x < cn; ++x) a = fmaf(sc[x], to_f(cache[static_cast<size_t>(key_row[x]) * row_elems + plane + g * d + c]), a);
+      acc[c] = a;
+    }
+    __syncthreads();
+  }
+  const float inv = out_scale / l_run;
+  for (int c = threadIdx.x; c < d; c += WA_THREADS) out[static_cast<long long>(t) * out_ld + h * d + c] = from_f<T>(acc[c] * inv);
+}
+
+// --------------------------------------------------------------------------------------------------------- recurrent scans
+// A block owns SCAN_THREADS / R columns of the d x dv state of one (sequence, head) and walks the sequence's new tokens in order (the
+// columns of these recurrences do not interact).  Thread (col, r) -- r varying fastest, R a power of two <= 32 -- holds rows r, r + R, ...
+// of its column in registers; sums over rows are finished by a butterfly over the R lanes.  The state is kept in global memory in thread
+// order ([column tile][RPT][SCAN_THREADS], opaque to everything but these kernels, coalesced); inputs of SCAN_CHUNK tokens at a time are
+// staged in shared memory.
+constexpr int SCAN_CHUNK = 8, SCAN_THREADS = 256;
+
+template <int R>
+__device__ __forceinline__ float lanes_sum(float v) {
+#pragma unroll
+  for (int o = R / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// q / k at columns q_col0 / k_col0 of proj (H x d each), v at v_col0 (H x dv); gates: pre-activations [T, 2 H] fp32 (input gate | forget
+// gate) without their biases.  state_S [slots, H, RPT * threads], state_n [slots, H, d], state_m [slots, H].  out fp32 [T, H dv].
+template <typename T, int RPT, int R>
+__global__ void __launch_bounds__(SCAN_THREADS)
+matrix_memory_scan_kernel(const T* __restrict__ proj, long long ld, int q_col0, int k_col0, int v_col0,
+                                          const float* __restrict__ gates, const float* __restrict__ bias_i, const float* __restrict__ bias_f,
+                                          float cap, const int4* __restrict__ seq_desc, float* __restrict__ state_S, float* __restrict__ state_n,
+                                          float* __restrict__ state_m, float* __restrict__ out, int H, int d, int dv) {
+  extern __shared__ float sm[];
+  const int4 sd = seq_desc[blockIdx.x];
+  const int h = blockIdx.y, tid = threadIdx.x;
+  constexpr int nthr = SCAN_THREADS;
+  const int col = blockIdx.z * (nthr / R) + tid / R, r = tid % R;
+  const bool live = col < dv;
+  float* qs = sm;                        // [CHUNK][d]
+  float* ks = qs + SCAN_CHUNK * d;       // [CHUNK][d]
+  float* vs = ks + SCAN_CHUNK * d;       // [CHUNK][dv]
+  float* gi = vs + SCAN_CHUNK * dv;      // [CHUNK] log input gate
+  float* gf = gi + SCAN_CHUNK;           // [CHUNK] log forget gate
+  float S[RPT], nn[RPT];
+  float m;
+  float* gS = state_S + ((static_cast<size_t>(sd.w) * H + h) * gridDim.z + blockIdx.z) * RPT * nthr;
+  float* gn = state_n + (static_cast<size_t>(sd.w) * H + h) * d;
+  if (sd.z > 0) {
+#pragma unroll
+    for (int ii = 0; ii < RPT; ++ii) {
+      S[ii] = gS[ii * nthr + tid];
+      const int i = r + R * ii;
+      nn[ii] = i < d ? gn[i] : 0.f;
+    }
+    m = state_m[sd.w * H + h];
+  } else {
+#pragma unroll
+    for (int ii = 0; ii < RPT; ++ii) S[ii] = nn[ii] = 0.f;
+    m = 0.f;
+  }
+  const float qscale = 1.f / sqrtf(static_cast<float>(d));
+  for (int t0 = 0; t0 < sd.y; t0 += SCAN_CHUNK) {
+    const int cn = min(SCAN_CHUNK, sd.y - t0);
+    __syncthreads();
+    for (int x = tid; x < cn * d; x += nthr) {
+      const long long row = static_cast<long long>(sd.x + t0 + x / d) * ld;
+      qs[x] = to_f(proj[row + q_col0 + h * d + x % d]) * qscale;
+      ks[x] = to_f(proj[row + k_col0 + h * d + x % d]);
+    }
+    for (int x = tid; x < cn * dv; x += nthr) vs[x] = to_f(proj[static_cast<long long>(sd.x + t0 + x / dv) * ld + v_col0 + h * dv + x % dv]);
+    for (int x = tid; x < cn; x += nthr) {
+      const float* gr = gates + static_cast<size_t>(sd.x + t0 + x) * 2 * H;
+      gi[x] = cap * tanhf((gr[h] + bias_i[h]) / cap);
+      gf[x] = logsigmoidf_(cap * tanhf((gr[H + h] + bias_f[h]) / cap));
+    }
+    __syncthreads();
+    for (int x = 0; x < cn; ++x) {
+      const float m_new = fmaxf(gf[x] + m, gi[x]);
+      const float a = expf(gf[x] + m - m_new), b = expf(gi[x] - m_new);
+      m = m_new;
+      const float v = live ? vs[x * dv + col] : 0.f;
+      float po = 0.f, pn = 0.f;
+#pragma unroll
+      for (int ii = 0; ii < RPT; ++ii) {
+        const int i = r + R * ii;
+        const float kk = i < d ? ks[x * d + i] : 0.f, qq = i < d ? qs[x * d + i] : 0.f;
+        const float bk = b * kk;
+        S[ii] = fmaf(a, S[ii], bk * v);
+        nn[ii] = fmaf(a, nn[ii], bk);
+        po = fmaf(S[ii], qq, po);
+        pn = fmaf(nn[ii], qq, pn);
+      }
+      po = lanes_sum<R>(po);
+      pn = lanes_sum<R>(pn);
+      if (live && r == 0) out[static_cast<size_t>(sd.x + t0 + x) * H * dv + h * dv + col] = po / (fmaxf(fabsf(pn), expf(-m)) + 1e-6f);
+    }
+  }
+#pragma unroll
+  for (int ii = 0; ii < RPT; ++ii) {
+    gS[ii * nthr + tid] = S[ii];
+    const int i = r + R * ii;
+    if (col == 0 && i < d) gn[i] = nn[ii];  // every column tile carries the same n and m; the first one keeps them
+  }
+  if (tid == 0 && blockIdx.z == 0) state_m[sd.w * H + h] = m;
+}
+
+// qn / kn fp32 [T, G d] (unit length; q already times d^-1/2), v fp32 [T, H dv], beta_pre fp32 [T, H] (before the sigmoid), a_pre fp32
+// [T, H d] (before dt_bias / softplus).  Head h reads q / k head h / (H / G).  out fp32 [T, H dv].
+template <int RPT, int R>
+__global__ void __launch_bounds__(SCAN_THREADS)
+delta_rule_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ v,
+                                       const float* __restrict__ beta_pre, const float* __restrict__ a_pre, const float* __restrict__ A_log,
+                                       const float* __restrict__ dt_bias, const int4* __restrict__ seq_desc, float* __restrict__ state_S,
+                                       float* __restrict__ out, int H, int G, int d, int dv) {
+  extern __shared__ float sm[];
+  const int4 sd = seq_desc[blockIdx.x];
+  const int h = blockIdx.y, g = h / (H / G), tid = threadIdx.x;
+  constexpr int nthr = SCAN_THREADS;
+  const int col = blockIdx.z * (nthr / R) + tid / R, r = tid % R;
+  const bool live = col < dv;
+  float* qs = sm;                        // [CHUNK][d]
+  float* ks = qs + SCAN_CHUNK * d;       // [CHUNK][d]
+  float* gs = ks + SCAN_CHUNK * d;       // [CHUNK][d] decays
+  float* vs = gs + SCAN_CHUNK * d;       // [CHUNK][dv]
+  float* bs = vs + SCAN_CHUNK * dv;      // [CHUNK]
+  float S[RPT];
+  float* gS = state_S + ((static_cast<size_t>(sd.w) * H + h) * gridDim.z + blockIdx.z) * RPT * nthr;
+#pragma unroll
+  for (int ii = 0; ii < RPT; ++ii) S[ii] = sd.z > 0 ? gS[ii * nthr + tid] : 0.f;
+  const float rate = expf(A_log[h]);
+  for (int t0 = 0; t0 < sd.y; t0 += SCAN_CHUNK) {
+    const int cn = min(SCAN_CHUNK, sd.y - t0);
+    __syncthreads();
+    for (int x = tid; x < cn * d; x += nthr) {
+      const size_t row = static_cast<size_t>(sd.x + t0 + x / d);
+      const int i = x % d;
+      qs[x] = qn[row * G * d + g * d + i];
+      ks[x] = kn[row * G * d + g * d + i];
+      gs[x] = expf(-rate * softplusf_(a_pre[row * H * d + h * d + i] + dt_bias[h * d + i]));
+    }
+    for (int x = tid; x < cn * dv; x += nthr) vs[x] = v[static_cast<size_t>(sd.x + t0 + x / dv) * H * dv + h * dv + x % dv];
+    for (int x = tid; x < cn; x += nthr) bs[x] = sigmoidf_(beta_pre[static_cast<size_t>(sd.x + t0 + x) * H + h]);
+    __syncthreads();
+    for (int x = 0; x < cn; ++x) {
+      float ps = 0.f;
+#pragma unroll
+      for (int ii = 0; ii < RPT; ++ii) {
+        const int i = r + R * ii;
+        if (i < d) {
+          S[ii] *= gs[x * d + i];
+          ps = fmaf(S[ii], ks[x * d + i], ps);
+        }
+      }
+      ps = lanes_sum<R>(ps);
+      const float u = live ? bs[x] * (vs[x * dv + col] - ps) : 0.f;
+      float po = 0.f;
+#pragma unroll
+      for (int ii = 0; ii < RPT; ++ii) {
+        const int i = r + R * ii;
+        if (i < d) {
+          S[ii] = fmaf(ks[x * d + i], u, S[ii]);
+          po = fmaf(S[ii], qs[x * d + i], po);
+        }
+      }
+      po = lanes_sum<R>(po);
+      if (live && r == 0) out[static_cast<size_t>(sd.x + t0 + x) * H * dv + h * dv + col] = po;
+    }
+  }
+#pragma unroll
+  for (int ii = 0; ii < RPT; ++ii) gS[ii * nthr + tid] = S[ii];
+}
+
+// One block per token.  proj row holds the q [G d], k [G d] and v [H dv] projections at q_col0 / k_col0 / v_col0; the kept rows of the
+// sequence are [taps - 1, 2 G d + H dv] (q | k | v channels).  Each goes through its short convolution and silu; q and k are then made unit
+// vectors per head (x / sqrt(sum x^2 + 1e-6)), q also times d^-1/2.  Outputs fp32.
+template <typename T>
+__global__ void delta_prepare_kernel(const T* __restrict__ proj, long long ld, int q_col0, int k_col0, int v_col0, const float* __restrict__ conv_q,
+                                     const float* __restrict__ conv_k, const float* __restrict__ conv_v, const T* __restrict__ state,
+                                     const int4* __restrict__ seq_desc, const int* __restrict__ tok_seq, float* __restrict__ qn,
+                                     float* __restrict__ kn, float* __restrict__ vo, int G, int H, int d, int dv, int taps) {
+  extern __shared__ float sm[];
+  const int t = blockIdx.x;
+  const int nqk = G * d, nv = H * dv, C = 2 * nqk + nv;
+  float* y = sm;             // [2 G d]: q then k
+  float* ss = sm + 2 * nqk;  // [2 G] sums of squares per head
+  const int4 sd = seq_desc[tok_seq[t]];
+  const int i = t - sd.x;
+  const T* st = state + static_cast<size_t>(sd.w) * (taps - 1) * C;
+  const T* u0 = proj + static_cast<long long>(sd.x) * ld;
+  for (int c = threadIdx.x; c < 2 * G; c += blockDim.x) ss[c] = 0.f;
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const int which = c < nqk ? 0 : (c < 2 * nqk ? 1 : 2);
+    const int cc = c - (which == 0 ? 0 : (which == 1 ? nqk : 2 * nqk));
+    const int col0 = which == 0 ? q_col0 : (which == 1 ? k_col0 : v_col0);
+    const float* w = (which == 0 ? conv_q : (which == 1 ? conv_k : conv_v)) + static_cast<size_t>(cc) * taps;
+    const float val = siluf_(conv_at(u0 + col0 + cc, ld, st + c, C, w, taps, i, sd.z));
+    if (which == 2) vo[static_cast<size_t>(t) * nv + cc] = val;
+    else {
+      y[c] = val;
+      atomicAdd(&ss[which * G + cc / d], val * val);
+    }
+  }
+  __syncthreads();
+  const float qscale = 1.f / sqrtf(static_cast<float>(d));
+  for (int c = threadIdx.x; c < 2 * nqk; c += blockDim.x) {
+    const int which = c < nqk ? 0 : 1, cc = c - which * nqk;
+    const float inv = 1.f / sqrtf(ss[which * G + cc / d] + 1e-6f);
+    if (which == 0) qn[static_cast<size_t>(t) * nqk + cc] = y[c] * inv * qscale;
+    else kn[static_cast<size_t>(t) * nqk + cc] = y[c] * inv;
+  }
+}
+
+// One warp per (token, head): out[t, col0 + h dv + c] = o / sqrt(mean_c(o^2) + eps) * w[h * w_stride + c] * sigmoid(gate[t, h dv + c]) * mult
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, int w_stride, const T* __restrict__ gate,
+                                      long long gate_ld, T* __restrict__ out, long long out_ld, int n_tokens, int H, int dv, float eps, float mult) {
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (gw >= n_tokens * H) return;
+  const int t = gw / H, h = gw % H;
+  const float* orow = o + (static_cast<size_t>(t) * H + h) * dv;
+  float s = 0.f;
+  for (int c = lane; c < dv; c += 32) s += orow[c] * orow[c];
+  s = warp_sum(s);
+  const float inv = 1.f / sqrtf(s / static_cast<float>(dv) + eps);
+  const T* gr = gate + static_cast<long long>(t) * gate_ld + h * dv;
+  T* dst = out + static_cast<long long>(t) * out_ld + h * dv;
+  for (int c = lane; c < dv; c += 32) dst[c] = from_f<T>(orow[c] * inv * w[h * w_stride + c] * sigmoidf_(to_f(gr[c])) * mult);
+}
+
+}  // namespace recur
+}  // namespace dsb
+
+using namespace dsb;
+using namespace dsb::recur;
+
+// Lanes per column (R), rows per thread (RPT, rounded up to 8 / 16 / 32 / 64) and column tiles of a d x dv state: about 8 rows per thread
+// (a short dependent chain per token); a block of SCAN_THREADS threads then covers SCAN_THREADS / R columns.
+static bool scan_shape(int d, int dv, int* R, int* RPT, int* tiles) {
+  if (d < 1 || dv < 1) return false;
+  int r = 1;
+  while (r < 32 && (d + r - 1) / r > 8) r <<= 1;
+  const int need = (d + r - 1) / r;
+  int rpt = 8;
+  while (rpt < need) rpt <<= 1;
+  const int cols = SCAN_THREADS / r;
+  *R = r;
+  *RPT = rpt;
+  *tiles = (dv + cols - 1) / cols;
+  return rpt <= 64;
+}
+
+// Floats of state_S per (slot, head) for a d x dv recurrent state (the layout is the scan kernels' own).
+DSB_EXPORT long long dsb200_scan_state_floats(int d, int dv) {
+  int R, RPT, tiles;
+  if (!scan_shape(d, dv, &R, &RPT, &tiles)) return -1;
+  return static_cast<long long>(tiles) * RPT * SCAN_THREADS;
+}
+
+#define SCAN_DISPATCH(RPTv, Rv, CALL) \
+  if (RPT == RPTv && R == Rv) { CALL(RPTv, Rv); launched = true; }
+#define SCAN_DISPATCH_ROW(RPTv, CALL)                                                                                         \
+  SCAN_DISPATCH(RPTv, 1, CALL) SCAN_DISPATCH(RPTv, 2, CALL) SCAN_DISPATCH(RPTv, 4, CALL) SCAN_DISPATCH(RPTv, 8, CALL)         \
+  SCAN_DISPATCH(RPTv, 16, CALL) SCAN_DISPATCH(RPTv, 32, CALL)
+#define SCAN_DISPATCH_ALL(CALL)                                                                                               \
+  do {                                                                                                                        \
+    SCAN_DISPATCH_ROW(8, CALL) SCAN_DISPATCH_ROW(16, CALL) SCAN_DISPATCH_ROW(32, CALL) SCAN_DISPATCH_ROW(64, CALL)            \
+  } while (0)
+
+// proj [T, ld] (dtype 0 = bf16, 1 = fp32) holds, per token, the projections a windowed attention mixer convolves: queries [H d] at
+// column q_col0 and keys [G d] at k_col0.  Per token: short convolution (weights fp32 [channels, taps], last column = current token,
+// earlier rows from the batch or from `state` [slots, taps - 1, (H + G) d]) -> the convolved keys go to plane 1 of the token's cache row
+// (they are the values); RMS norm over the whole q / whole k projection with plain weights norm_q / norm_k; rotation of pairs (2i, 2i + 1)
+// of the first rot_dims entries of every head by pos * freq[i] (freq: doubles on the device); q to q_out [T, q_ld], k to cache plane 0.
+// cache [blocks, 2, block_size, G, d].  Call dsb200_conv_state_update afterwards.
+DSB_EXPORT int dsb200_window_qk_prepare(const void* proj, long long ld, int q_col0, int k_col0, const float* conv_q, const float* conv_k,
+                                        const float* norm_q, const float* norm_k, const void* state, const int* seq_desc, const int* tok_seq,
+                                        const int* tok_pos, const int* block_table, int bt_stride, int block_size, void* cache, void* q_out,
+                                        long long q_ld, const double* freq, int n_tokens, int H, int G, int d, int taps, int rot_dims, float eps,
+                                        int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return DSB_OK;
+  DSB_REQUIRE(H >= 1 && G >= 1 && H % G == 0 && d % 2 == 0 && rot_dims % 2 == 0 && rot_dims <= d && taps >= 1,
+              "window_qk_prepare: heads %d / %d, head size %d, rotated %d, taps %d", H, G, d, rot_dims, taps);
+  const size_t smem = (static_cast<size_t>(H + G) * d + rot_dims) * sizeof(float);
+  DSB_REQUIRE(smem <= 200 * 1024, "window_qk_prepare: (H + G) d = %d does not fit shared memory", (H + G) * d);
+  const int block = (H + G) * d >= 2048 ? 512 : 256;
+#define LAUNCH(T)                                                                                                                          \
+  do {                                                                                                                                     \
+    if (smem > 48 * 1024) DSB_CHECK_CUDA(cudaFuncSetAttribute(window_qk_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    window_qk_prepare_kernel<T><<<n_tokens, block, smem, stream>>>((const T*)proj, ld, q_col0, k_col0, conv_q, conv_k, norm_q, norm_k,     \
+                                                                   (const T*)state, (const int4*)seq_desc, tok_seq, tok_pos, block_table,   \
+                                                                   bt_stride, block_size, (T*)cache, (T*)q_out, q_ld, freq, H, G, d, taps,  \
+                                                                   rot_dims, eps);                                                         \
+  } while (0)
+  if (dtype == 0) LAUNCH(bf16);
+  else LAUNCH(float);
+#undef LAUNCH
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// Columns st_col0 .. st_col0 + C of state [slots, taps - 1, st_ld] <- the last taps - 1 projected rows (columns col0 .. col0 + C of proj
+// [T, ld]) of every sequence of the batch, older rows shifting up when the step brought fewer than taps - 1 tokens.  Run after the
+// kernels that read the state.
+DSB_EXPORT int dsb200_conv_state_update(const void* proj, long long ld, int col0, void* state, int st_ld, int st_col0, const int* seq_desc,
+                                        int n_seqs, int C, int taps, int dtype, cudaStream_t stream) {
+  if (n_seqs == 0 || taps <= 1 || C == 0) return DSB_OK;
+  const dim3 grid((C + 255) / 256, n_seqs);
+  if (dtype == 0) conv_state_update_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)proj, ld, col0, (bf16*)state, st_ld, st_col0, (const int4*)seq_desc, C, taps);
+  else conv_state_update_kernel<float><<<grid, 256, 0, stream>>>((const float*)proj, ld, col0, (float*)state, st_ld, st_col0, (const int4*)seq_desc, C, taps);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// out[t, h d + c] = out_scale * sum_j softmax_j(scale q_h . k_j) v_j[c] over the keys j <= pos(t) of the token's sequence with
+// pos - j < window or j < keep_first.  q [T, q_ld] (H heads of d), cache [blocks, 2, block_size, G, d] (plane 0 keys, 1 values), query head
+// h reads key/value head h / (H / G); out [T, out_ld].  CUDA cores, fp32 scores and accumulation, any sizes; dtype 0 = bf16, 1 = fp32.
+DSB_EXPORT int dsb200_window_attention(const void* q, long long q_ld, const void* cache, const int* tok_seq, const int* tok_pos,
+                                       const int* block_table, int bt_stride, int block_size, void* out, long long out_ld, int n_tokens, int H,
+                                       int G, int d, int window, int keep_first, float scale, float out_scale, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return DSB_OK;
+  DSB_REQUIRE(H % G == 0 && window >= 1 && keep_first >= 0 && d <= 4096, "window_attention: heads %d / %d, window %d, kept %d, head size %d", H, G,
+              window, keep_first, d);
+  const dim3 grid(n_tokens, H);
+  const size_t smem = 2 * static_cast<size_t>(d) * sizeof(float);
+  if (dtype == 0)
+    window_attention_kernel<bf16><<<grid, WA_THREADS, smem, stream>>>((const bf16*)q, q_ld, (const bf16*)cache, tok_seq, tok_pos, block_table,
+                                                                      bt_stride, block_size, (bf16*)out, out_ld, H, G, d, window, keep_first,
+                                                                      scale, out_scale);
+  else
+    window_attention_kernel<float><<<grid, WA_THREADS, smem, stream>>>((const float*)q, q_ld, (const float*)cache, tok_seq, tok_pos, block_table,
+                                                                       bt_stride, block_size, (float*)out, out_ld, H, G, d, window, keep_first,
+                                                                       scale, out_scale);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// Matrix memory with exponential gating, per sequence and head, over the new tokens in order:
+//   i = cap tanh((gates[t, h] + bias_i[h]) / cap),  f = logsigmoid(cap tanh((gates[t, H + h] + bias_f[h]) / cap)),
+//   m' = max(f + m, i);  S <- exp(f + m - m') S + exp(i - m') k v^T;  n likewise with k;  out = S^T q / (max(|n . q|, exp(-m')) + 1e-6)
+// with q = proj[q_col0 ..] * d^-1/2, k, v from proj [T, ld] (dtype 0 = bf16, 1 = fp32); gates fp32 [T, 2 H]; out fp32 [T, H dv].
+// state_S [slots, H, dsb200_scan_state_floats(d, dv)], state_n [slots, H, d], state_m [slots, H], all fp32; a sequence at position 0 starts
+// from zeros (m = 0).
+DSB_EXPORT int dsb200_matrix_memory_scan(const void* proj, long long ld, int q_col0, int k_col0, int v_col0, const float* gates,
+                                         const float* bias_i, const float* bias_f, float cap, const int* seq_desc, float* state_S,
+                                         float* state_n, float* state_m, float* out, int n_seqs, int H, int d, int dv, int dtype,
+                                         cudaStream_t stream) {
+  if (n_seqs == 0) return DSB_OK;
+  int R, RPT, tiles;
+  DSB_REQUIRE(scan_shape(d, dv, &R, &RPT, &tiles), "matrix_memory_scan: a %d x %d state per head is not supported", d, dv);
+  const int threads = SCAN_THREADS;
+  const size_t smem = (static_cast<size_t>(SCAN_CHUNK) * (2 * d + dv + 2)) * sizeof(float);
+  DSB_REQUIRE(smem <= 48 * 1024, "matrix_memory_scan: head sizes %d / %d do not fit shared memory", d, dv);
+  const dim3 grid(n_seqs, H, tiles);
+  bool launched = false;
+#define CALL(RPTv, Rv)                                                                                                                    \
+  do {                                                                                                                                    \
+    if (dtype == 0)                                                                                                                       \
+      matrix_memory_scan_kernel<bf16, RPTv, Rv><<<grid, threads, smem, stream>>>((const bf16*)proj, ld, q_col0, k_col0, v_col0, gates, bias_i, \
+                                                                                 bias_f, cap, (const int4*)seq_desc, state_S, state_n,    \
+                                                                                 state_m, out, H, d, dv);                                 \
+    else                                                                                                                                  \
+      matrix_memory_scan_kernel<float, RPTv, Rv><<<grid, threads, smem, stream>>>((const float*)proj, ld, q_col0, k_col0, v_col0, gates,      \
+                                                                                  bias_i, bias_f, cap, (const int4*)seq_desc, state_S,    \
+                                                                                  state_n, state_m, out, H, d, dv);                       \
+  } while (0)
+  SCAN_DISPATCH_ALL(CALL);
+#undef CALL
+  DSB_REQUIRE(launched, "matrix_memory_scan: no kernel for %d rows per thread x %d lanes", RPT, R);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// Inputs of the delta-rule scan from the fused projection proj [T, ld] (dtype 0 = bf16, 1 = fp32): q [G d] at q_col0, k [G d] at k_col0, v
+// [H dv] at v_col0, each through its short convolution (weights fp32 [channels, taps]; earlier rows from the batch or from `state`
+// [slots, taps - 1, 2 G d + H dv]) and silu; q and k then scaled to unit length per head (x / sqrt(sum x^2 + 1e-6)), q also by d^-1/2.
+// qn, kn fp32 [T, G d]; vo fp32 [T, H dv].  Call dsb200_conv_state_update (three column ranges) afterwards.
+DSB_EXPORT int dsb200_delta_prepare(const void* proj, long long ld, int q_col0, int k_col0, int v_col0, const float* conv_q, const float* conv_k,
+                                    const float* conv_v, const void* state, const int* seq_desc, const int* tok_seq, float* qn, float* kn,
+                                    float* vo, int n_tokens, int G, int H, int d, int dv, int taps, int dtype, cudaStream_t stream) {
+  if (n_tokens == 0) return DSB_OK;
+  const size_t smem = (2 * static_cast<size_t>(G) * d + 2 * G) * sizeof(float);
+  DSB_REQUIRE(smem <= 200 * 1024, "delta_prepare: 2 G d = %d does not fit shared memory", 2 * G * d);
+  const int block = 2 * G * d + H * dv >= 2048 ? 512 : 256;
+#define LAUNCH(T)                                                                                                                       \
+  do {                                                                                                                                  \
+    if (smem > 48 * 1024) DSB_CHECK_CUDA(cudaFuncSetAttribute(delta_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    delta_prepare_kernel<T><<<n_tokens, block, smem, stream>>>((const T*)proj, ld, q_col0, k_col0, v_col0, conv_q, conv_k, conv_v,        \
+                                                               (const T*)state, (const int4*)seq_desc, tok_seq, qn, kn, vo, G, H, d, dv, taps); \
+  } while (0)
+  if (dtype == 0) LAUNCH(bf16);
+  else LAUNCH(float);
+#undef LAUNCH
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// Gated delta rule with one decay per head and key channel, per sequence and head over the new tokens in order:
+//   g = exp(-exp(A_log[h]) softplus(a_pre[t, h, :] + dt_bias[h, :]));  S <- diag(g) S;  u = sigmoid(beta_pre[t, h]) (v - S^T k);
+//   S <- S + k u^T;  out = S^T q
+// qn, kn fp32 [T, G d] (head h reads q / k head h / (H / G)), v fp32 [T, H dv], beta_pre fp32 [T, H], a_pre fp32 [T, H d]; out fp32 [T, H dv];
+// state_S [slots, H, dsb200_scan_state_floats(d, dv)] fp32; a sequence at position 0 starts from zeros.
+DSB_EXPORT int dsb200_delta_rule_scan(const float* qn, const float* kn, const float* v, const float* beta_pre, const float* a_pre,
+                                      const float* A_log, const float* dt_bias, const int* seq_desc, float* state_S, float* out, int n_seqs,
+                                      int H, int G, int d, int dv, cudaStream_t stream) {
+  if (n_seqs == 0) return DSB_OK;
+  int R, RPT, tiles;
+  DSB_REQUIRE(H % G == 0 && scan_shape(d, dv, &R, &RPT, &tiles), "delta_rule_scan: heads %d / %d, a %d x %d state per head is not supported", H, G, d, dv);
+  const int threads = SCAN_THREADS;
+  const size_t smem = (static_cast<size_t>(SCAN_CHUNK) * (3 * d + dv + 1)) * sizeof(float);
+  DSB_REQUIRE(smem <= 48 * 1024, "delta_rule_scan: head sizes %d / %d do not fit shared memory", d, dv);
+  const dim3 grid(n_seqs, H, tiles);
+  bool launched = false;
+#define CALL(RPTv, Rv)                                                                                                                       \
+  delta_rule_scan_kernel<RPTv, Rv><<<grid, threads, smem, stream>>>(qn, kn, v, beta_pre, a_pre, A_log, dt_bias, (const int4*)seq_desc, state_S, \
+                                                                    out, H, G, d, dv)
+  SCAN_DISPATCH_ALL(CALL);
+#undef CALL
+  DSB_REQUIRE(launched, "delta_rule_scan: no kernel for %d rows per thread x %d lanes", RPT, R);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}
+
+// out[t, h dv + c] = o[t, h, c] / sqrt(mean_c o[t, h, :]^2 + eps) * w[h * w_stride + c] * sigmoid(gate[t, h dv + c]) * mult.  o fp32
+// [T, H dv]; w fp32 (w_stride = dv: one weight row per head, 0: one row shared by the heads); gate [T, gate_ld] and out [T, out_ld] in the
+// activation dtype (0 = bf16, 1 = fp32).
+DSB_EXPORT int dsb200_head_norm_gate(const float* o, const float* w, int w_stride, const void* gate, long long gate_ld, void* out, long long out_ld,
+                                     int n_tokens, int H, int dv, float eps, float mult, int dtype, cudaStream_t stream) {
+  const long long warps = static_cast<long long>(n_tokens) * H;
+  if (warps == 0) return DSB_OK;
+  const int wpb = 8;
+  const int grid = static_cast<int>((warps + wpb - 1) / wpb);
+  if (dtype == 0)
+    head_norm_gate_kernel<bf16><<<grid, wpb * 32, 0, stream>>>(o, w, w_stride, (const bf16*)gate, gate_ld, (bf16*)out, out_ld, n_tokens, H, dv, eps, mult);
+  else
+    head_norm_gate_kernel<float><<<grid, wpb * 32, 0, stream>>>(o, w, w_stride, (const float*)gate, gate_ld, (float*)out, out_ld, n_tokens, H, dv, eps, mult);
+  DSB_CHECK_CUDA(cudaGetLastError());
+  return DSB_OK;
+}

@@ -35,7 +35,9 @@ class InferenceEngineV2:
         else:
             kv_cfg = KVCacheConfig(block_size=block,
                                    cache_shape=(spec.num_layers, self._model.hkv, spec.head_dim), cache_dtype="bf16")
-        self._state_manager = DSStateManager(engine_config.state_manager, kv_cfg, base_mp_group=self._tp_group)
+        # fixed-size per-sequence state (recurrent memories, convolution tails) of models that have it: one slot per trackable sequence
+        state_specs = self._model.state_config() if hasattr(self._model, "state_config") else None
+        self._state_manager = DSStateManager(engine_config.state_manager, kv_cfg, base_mp_group=self._tp_group, state_specs=state_specs)
         self._batch = RaggedBatchWrapper(engine_config.state_manager)
         self._batch.set_block_table_shape(self._state_manager.max_blocks_per_seq)
 

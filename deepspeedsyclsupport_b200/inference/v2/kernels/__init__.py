@@ -227,7 +227,7 @@ def moe_gather(moe_out, scores, mapped_slots):
 # for any width in bf16 or fp32.  Device only: these ops have no host form (their oracles live with the tests).
 native.register_sigs({
     "dsb200_embed_sinusoid": "pp i pp p ii p",
-    "dsb200_sandwich_norm": "pp i p f p f p i pp ii f p",
+    "dsb200_sandwich_norm": "pp i p ff p f p i pp ii f i p",
     "dsb200_latent_norm_append": "p i pp pp ppp iiii ii f i p",
     "dsb200_paged_flash_latent": "p i ll pp ppp iiiiii f ii p i p",
     "dsb200_gate_heads": "pp l p iii i p",
@@ -236,8 +236,8 @@ native.register_sigs({
     "dsb200_sigmoid_gate_mul": "p l p l l i i p",
     "dsb200_clamped_swish_gate": "pp l i fff i p",
     "dsb200_softcap": "p l l i f p",
-    "dsb200_grouped_topk_gating": "pppppp iiiiii p",
-    "dsb200_moe_scatter_rows": "ppppppp iiii i p",
+    "dsb200_grouped_topk_gating": "pppppp iiiiiii p",
+    "dsb200_moe_scatter_rows": "ppppppp iiii i p p",
     "dsb200_moe_gather_rows": "pppp iii i p",
     "dsb200_moe_gemm_rows": "pppp iiii i p",
 }, restype_long=("dsb200_latent_attention_scratch_floats", ))
@@ -258,7 +258,7 @@ def sinusoid_frequencies(dim, base=10000.0, device=None):
 
 
 def embed_sinusoid(ids, table, tok_pos, freq):
-    """fp32 [T, dim]: table[ids] + (sin(p f_0), cos(p f_0), sin(p f_1), ...)."""
+    """fp32 [T, dim]: table[ids] + (sin(p f_0), cos(p f_0), sin(p f_1), ...); `freq` None: the table rows alone."""
     T, dim = ids.numel(), table.shape[1]
     out = torch.empty(T, dim, dtype=torch.float32, device=table.device)
     native.check(native.lib().dsb200_embed_sinusoid(native.ptr(ids), native.ptr(table), _dt(table), native.ptr(tok_pos), native.ptr(freq),
@@ -266,21 +266,24 @@ def embed_sinusoid(ids, table, tok_pos, freq):
     return out
 
 
-def sandwich_norm(x, y=None, wb=None, ob=0.0, w=None, o=0.0, eps=1e-6, out_dtype=torch.bfloat16, rows=None, fp32_copy=False):
-    """On the fp32 residual x [T, dim], in place: x += rms_norm(y) * (wb + ob) when a branch output y is given; returns
-    rms_norm(x) * (w + o) in `out_dtype` when w is given (else None).  `rows` (int32 indices): normalise only those rows of x
-    (no branch then); the result has one row per index.  `fp32_copy`: also return the normed values before their rounding to
-    `out_dtype` -> (out, out_fp32); for an fp32 `out_dtype` both are the same tensor."""
+def sandwich_norm(x, y=None, wb=None, ob=0.0, w=None, o=0.0, eps=1e-6, out_dtype=torch.bfloat16, rows=None, fp32_copy=False, y_mult=1.0,
+                  plain_out=False):
+    """On the fp32 residual x [T, dim], in place: x += y_mult * rms_norm(y) * (wb + ob) when a branch output y is given; returns
+    rms_norm(x) * (w + o) in `out_dtype` when w is given, the stream itself in `out_dtype` when `plain_out` (blocks whose sublayers
+    read the stream unnormed), else None.  `rows` (int32 indices): normalise only those rows of x (no branch then); the result has
+    one row per index.  `fp32_copy`: also return the normed values before their rounding to `out_dtype` -> (out, out_fp32); for an
+    fp32 `out_dtype` both are the same tensor."""
     assert x.dtype == torch.float32 and x.is_contiguous() and x.is_cuda
+    assert not (plain_out and (w is not None or fp32_copy))
     n = x.shape[0] if rows is None else rows.numel()
-    out = torch.empty(n, x.shape[1], dtype=out_dtype, device=x.device) if w is not None else None
+    out = torch.empty(n, x.shape[1], dtype=out_dtype, device=x.device) if (w is not None or plain_out) else None
     out32 = torch.empty(n, x.shape[1], dtype=torch.float32, device=x.device) if (fp32_copy and w is not None and out_dtype != torch.float32) else None
     if y is not None:
         assert y.shape == x.shape
         y = y if y.is_contiguous() else y.contiguous()  # a GEMM output whose rows were padded to the TMA stride (odd widths only)
     native.check(native.lib().dsb200_sandwich_norm(native.ptr(x), native.ptr(y), _dt(y) if y is not None else 0, native.ptr(wb), float(ob),
-                                                   native.ptr(w), float(o), native.ptr(out), _DT[out_dtype], native.ptr(out32), native.ptr(rows), n,
-                                                   x.shape[1], float(eps), native.stream_ptr()))
+                                                   float(y_mult), native.ptr(w), float(o), native.ptr(out), _DT[out_dtype], native.ptr(out32),
+                                                   native.ptr(rows), n, x.shape[1], float(eps), int(plain_out), native.stream_ptr()))
     if fp32_copy:
         return out, (out32 if out32 is not None else out)
     return out
@@ -393,9 +396,10 @@ def softcap_(logits, cap):
     return logits
 
 
-def grouped_topk_gating(logits, k, correction=None, groups=1, keep=1, normalize=False):
+def grouped_topk_gating(logits, k, correction=None, groups=1, keep=1, normalize=False, sigmoid_scores=False):
     """Router with a selection bias and contiguous expert groups (see csrc/ragged/latent_ops.cu).  logits [T, E] fp32 ->
-    (expert_counts [E] int32, scores [T, k] fp32, assignments [T, k] int32, offsets [T, k] int32), as `top_k_gating`."""
+    (expert_counts [E] int32, scores [T, k] fp32, assignments [T, k] int32, offsets [T, k] int32), as `top_k_gating`.
+    `sigmoid_scores`: an expert's score is the sigmoid of its own logit instead of its softmax probability."""
     assert logits.dtype == torch.float32 and logits.is_cuda and logits.is_contiguous()
     T, E = logits.shape
     counts = torch.zeros(E, dtype=torch.int32, device=logits.device)
@@ -404,12 +408,12 @@ def grouped_topk_gating(logits, k, correction=None, groups=1, keep=1, normalize=
     off = torch.empty(T, k, dtype=torch.int32, device=logits.device)
     native.check(native.lib().dsb200_grouped_topk_gating(native.ptr(logits), native.ptr(correction), native.ptr(counts), native.ptr(scores),
                                                          native.ptr(asg), native.ptr(off), T, E, k, groups, keep, int(normalize),
-                                                         native.stream_ptr()))
+                                                         int(sigmoid_scores), native.stream_ptr()))
     return counts, scores, asg, off
 
 
-def moe_scatter_rows(x, counts, assignments, offsets):
-    """`moe_scatter` for any width and bf16 / fp32 rows."""
+def moe_scatter_rows(x, counts, assignments, offsets, row_scale=None):
+    """`moe_scatter` for any width and bf16 / fp32 rows.  `row_scale` (fp32 [T, k]): copy k of token t is multiplied by it."""
     T, dim = x.shape
     k, E = assignments.shape[1], counts.numel()
     assert x.is_contiguous()
@@ -418,12 +422,12 @@ def moe_scatter_rows(x, counts, assignments, offsets):
     slots = torch.empty(T, k, dtype=torch.int32, device=x.device)
     native.check(native.lib().dsb200_moe_scatter_rows(native.ptr(x), native.ptr(counts), native.ptr(assignments), native.ptr(offsets),
                                                       native.ptr(cumsum), native.ptr(moe_in), native.ptr(slots), T, E, dim, k, _dt(x),
-                                                      native.stream_ptr()), 2)
+                                                      native.ptr(row_scale), native.stream_ptr()), 2)
     return moe_in, cumsum, slots
 
 
 def moe_gather_rows(moe_out, scores, mapped_slots):
-    """fp32 [T, dim]: sum_k scores[t, k] * moe_out[mapped_slots[t, k]]."""
+    """fp32 [T, dim]: sum_k scores[t, k] * moe_out[mapped_slots[t, k]] (`scores` None: the plain sum)."""
     T, k = mapped_slots.shape
     assert moe_out.is_contiguous()
     out = torch.empty(T, moe_out.shape[1], dtype=torch.float32, device=moe_out.device)
@@ -440,4 +444,112 @@ def moe_gemm_rows(x, w, cumsum):
     out = torch.empty(R, N, dtype=x.dtype, device=x.device)
     native.check(native.lib().dsb200_moe_gemm_rows(native.ptr(x), native.ptr(w), native.ptr(out), native.ptr(cumsum), R, N, K, E, _dt(x),
                                                    native.stream_ptr()))
+    return out
+
+
+# ---- kernels of csrc/ragged/recurrent_ops.cu: short convolutions with per-sequence state, windowed attention that keeps the first
+# tokens visible, recurrent matrix memories.  Device only (their oracles live with the tests).  `seq_desc` is the batch's
+# [n_seqs, 4] int32 (first row, new tokens, tokens seen before, state slot).
+native.register_sigs({
+    "dsb200_scan_state_floats": "ii",
+    "dsb200_window_qk_prepare": "p l ii pppp p ppp p ii pp l p iiiiii f i p",
+    "dsb200_conv_state_update": "p l i p ii p iii i p",
+    "dsb200_window_attention": "p l p ppp ii p l iiiiii ff i p",
+    "dsb200_matrix_memory_scan": "p l iii ppp f p ppp p iiii i p",
+    "dsb200_delta_prepare": "p l iii ppp p pp ppp iiiiii i p",
+    "dsb200_delta_rule_scan": "ppppp pp p pp iiiii p",
+    "dsb200_head_norm_gate": "pp i p l p l iii ff i p",
+}, restype_long=("dsb200_scan_state_floats", ))
+
+
+def scan_state_floats(d, dv):
+    """fp32 values per (slot, head) of a d x dv recurrent state in the scan kernels' own layout."""
+    n = native.lib().dsb200_scan_state_floats(int(d), int(dv))
+    if n < 0:
+        raise native.NativeError(f"a {d} x {dv} recurrent state per head is not supported")
+    return int(n)
+
+
+def window_qk_prepare(proj, q_col0, k_col0, conv_q, conv_k, norm_q, norm_k, state, seq_desc, tok_seq, tok_pos, block_table, cache, q_out, freq,
+                      H, G, d, taps, rot_dims, eps):
+    """Short convolution of the query / key projections held in columns q_col0 / k_col0 of proj [T, ld], whole-projection RMS norms,
+    interleaved rotary on the first `rot_dims` entries of every head; the convolved keys go to cache plane 1 (they are the values), the
+    finished keys to plane 0 and the queries to q_out [T, >= H d].  cache [blocks, 2, block_size, G, d].  Follow with `conv_state_update`."""
+    T = proj.shape[0]
+    assert proj.stride(1) == 1 and cache.is_contiguous() and cache.dtype == proj.dtype and q_out.dtype == proj.dtype and q_out.stride(1) == 1
+    native.check(native.lib().dsb200_window_qk_prepare(native.ptr(proj), proj.stride(0), q_col0, k_col0, native.ptr(conv_q), native.ptr(conv_k),
+                                                       native.ptr(norm_q), native.ptr(norm_k), native.ptr(state), native.ptr(seq_desc),
+                                                       native.ptr(tok_seq), native.ptr(tok_pos), native.ptr(block_table), block_table.stride(0),
+                                                       cache.shape[2], native.ptr(cache), native.ptr(q_out), q_out.stride(0), native.ptr(freq), T,
+                                                       H, G, d, taps, rot_dims, float(eps), _dt(proj), native.stream_ptr()))
+    return q_out
+
+
+def conv_state_update(proj, col0, n_cols, state, st_col0, seq_desc, n_seqs, taps):
+    """state [slots, taps - 1, C] columns st_col0 .. + n_cols <- the last taps - 1 rows of columns col0 .. + n_cols of proj, per sequence."""
+    if taps <= 1:
+        return
+    assert state.is_contiguous() and state.dtype == proj.dtype and state.shape[1] == taps - 1
+    native.check(native.lib().dsb200_conv_state_update(native.ptr(proj), proj.stride(0), col0, native.ptr(state), state.shape[2], st_col0,
+                                                       native.ptr(seq_desc), n_seqs, n_cols, taps, _dt(proj), native.stream_ptr()))
+
+
+def window_attention(q, cache, tok_seq, tok_pos, block_table, out, H, G, d, window, keep_first, scale, out_scale=1.0):
+    """CUDA-core attention over the paged cache [blocks, 2, block_size, G, d]: a query at position p sees the keys j <= p with
+    p - j < window or j < keep_first.  q [T, >= H d], out [T, >= H d] (views with unit column stride); fp32 softmax and accumulation."""
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and cache.is_contiguous() and q.dtype == cache.dtype == out.dtype
+    native.check(native.lib().dsb200_window_attention(native.ptr(q), q.stride(0), native.ptr(cache), native.ptr(tok_seq), native.ptr(tok_pos),
+                                                      native.ptr(block_table), block_table.stride(0), cache.shape[2], native.ptr(out),
+                                                      out.stride(0), T, H, G, d, int(window), int(keep_first), float(scale), float(out_scale),
+                                                      _dt(q), native.stream_ptr()))
+    return out
+
+
+def matrix_memory_scan(proj, q_col0, k_col0, v_col0, gates, bias_i, bias_f, cap, seq_desc, n_seqs, state_S, state_n, state_m, H, d, dv):
+    """Matrix memory with exponential gating over every sequence's new tokens -> fp32 [T, H dv] read-outs (before the head norm)."""
+    T = proj.shape[0]
+    assert proj.stride(1) == 1 and gates.dtype == torch.float32 and gates.is_contiguous() and gates.shape == (T, 2 * H)
+    out = torch.empty(T, H * dv, dtype=torch.float32, device=proj.device)
+    native.check(native.lib().dsb200_matrix_memory_scan(native.ptr(proj), proj.stride(0), q_col0, k_col0, v_col0, native.ptr(gates),
+                                                        native.ptr(bias_i), native.ptr(bias_f), float(cap), native.ptr(seq_desc),
+                                                        native.ptr(state_S), native.ptr(state_n), native.ptr(state_m), native.ptr(out), n_seqs, H,
+                                                        d, dv, _dt(proj), native.stream_ptr()))
+    return out
+
+
+def delta_prepare(proj, q_col0, k_col0, v_col0, conv_q, conv_k, conv_v, state, seq_desc, tok_seq, G, H, d, dv, taps):
+    """Short convolution + silu of the q / k / v projections, q and k to unit length per head (q also times d^-1/2) ->
+    fp32 (q [T, G d], k [T, G d], v [T, H dv]).  Follow with `conv_state_update`."""
+    T = proj.shape[0]
+    assert proj.stride(1) == 1
+    qn = torch.empty(T, G * d, dtype=torch.float32, device=proj.device)
+    kn = torch.empty(T, G * d, dtype=torch.float32, device=proj.device)
+    vo = torch.empty(T, H * dv, dtype=torch.float32, device=proj.device)
+    native.check(native.lib().dsb200_delta_prepare(native.ptr(proj), proj.stride(0), q_col0, k_col0, v_col0, native.ptr(conv_q), native.ptr(conv_k),
+                                                   native.ptr(conv_v), native.ptr(state), native.ptr(seq_desc), native.ptr(tok_seq), native.ptr(qn),
+                                                   native.ptr(kn), native.ptr(vo), T, G, H, d, dv, taps, _dt(proj), native.stream_ptr()))
+    return qn, kn, vo
+
+
+def delta_rule_scan(qn, kn, v, beta_pre, a_pre, A_log, dt_bias, seq_desc, n_seqs, state_S, H, G, d, dv):
+    """Gated delta rule with per-channel decays over every sequence's new tokens -> fp32 [T, H dv] read-outs."""
+    T = qn.shape[0]
+    for t in (qn, kn, v, beta_pre, a_pre):
+        assert t.dtype == torch.float32 and t.is_contiguous()
+    out = torch.empty(T, H * dv, dtype=torch.float32, device=qn.device)
+    native.check(native.lib().dsb200_delta_rule_scan(native.ptr(qn), native.ptr(kn), native.ptr(v), native.ptr(beta_pre), native.ptr(a_pre),
+                                                     native.ptr(A_log), native.ptr(dt_bias), native.ptr(seq_desc), native.ptr(state_S),
+                                                     native.ptr(out), n_seqs, H, G, d, dv, native.stream_ptr()))
+    return out
+
+
+def head_norm_gate(o, w, gate, out, H, dv, eps, mult=1.0, shared_weight=False):
+    """out[:, h dv + c] = rms_norm_over_c(o[:, h, :]) * w * sigmoid(gate) * mult; o fp32 [T, H dv]; w fp32 [H dv] or (shared) [dv];
+    gate / out: views [T, >= H dv] of the activation dtype with unit column stride."""
+    T = o.shape[0]
+    assert o.dtype == torch.float32 and o.is_contiguous() and gate.stride(1) == 1 and out.stride(1) == 1 and gate.dtype == out.dtype
+    native.check(native.lib().dsb200_head_norm_gate(native.ptr(o), native.ptr(w), 0 if shared_weight else dv, native.ptr(gate), gate.stride(0),
+                                                    native.ptr(out), out.stride(0), T, H, dv, float(eps), float(mult), _dt(out),
+                                                    native.stream_ptr()))
     return out

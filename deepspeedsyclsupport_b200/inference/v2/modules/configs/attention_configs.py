@@ -82,3 +82,49 @@ class DSLatentAttentionConfig(DSModuleConfig):
         if self.kv_rank > 1024:
             raise ValueError("the latent attention kernels hold a latent row of at most 1024 values")
         return self
+
+
+class RotaryScalingConfig(DeepSpeedConfigModel):
+    """Slows the long-wavelength rotary frequencies down: a frequency f with wavelength l = 2 pi / f is kept when l < original / high,
+    divided by `factor` when l > original / low, and blended linearly in (original / l - low) / (high - low) in between."""
+    factor: float
+    low: float
+    high: float
+    original: float
+
+
+class DSWindowedAttentionConfig(DSModuleConfig):
+    """Attention whose queries and keys pass a short causal convolution over time, an RMS norm over the whole projection and an
+    interleaved partial rotation, whose values ARE the convolved keys (no value projection), and whose mask is a sliding window that
+    also keeps the first tokens of the sequence: query i sees key j <= i when i - j < window or j < keep_first."""
+    n_heads_q: int
+    n_heads_kv: int
+    head_size: int
+    conv_taps: int  # the last taps - 1 projected rows of a sequence are state
+    window: int
+    keep_first: int = 0
+    scale: float  # softmax scale (given, not derived from the head size)
+    rotate_dim: int = 0  # entries per head that are rotated (pairs (2i, 2i + 1)); 0 = no rotation
+    theta_base: float = 10_000.0
+    rotary_scaling: Optional[RotaryScalingConfig] = None
+    eps: float = 1e-6  # of the query / key norms
+    out_scale: float = 1.0  # the result is multiplied by this before it is rounded (mixers that are summed with weights)
+    max_sequences: int
+    input_dtype: DtypeEnum = DtypeEnum.bf16
+    output_dtype: DtypeEnum = DtypeEnum.bf16
+
+    @model_validator(mode="after")
+    def _consistent(self):
+        if self.n_heads_q <= 0 or self.n_heads_kv <= 0 or self.n_heads_q % self.n_heads_kv != 0:
+            raise ValueError(f"n_heads_q ({self.n_heads_q}) must be a positive multiple of n_heads_kv ({self.n_heads_kv})")
+        if self.head_size <= 0 or self.head_size % 2 != 0:
+            raise ValueError(f"head_size must be positive and even, got {self.head_size}")
+        if not (0 <= self.rotate_dim <= self.head_size and self.rotate_dim % 2 == 0):
+            raise ValueError(f"rotate_dim must be even and at most head_size ({self.head_size}), got {self.rotate_dim}")
+        if self.conv_taps < 1 or self.window < 1 or self.keep_first < 0:
+            raise ValueError("conv_taps and window must be at least 1, keep_first at least 0")
+        return self
+
+    @property
+    def group_size(self) -> int:
+        return self.n_heads_q // self.n_heads_kv

@@ -15,3 +15,5 @@ class DSEmbeddingsConfig(DSModuleConfig):
     # not None: a fixed sinusoidal position vector is added (entry 2i = sin(p base^(-2i/dim)), entry 2i+1 = cos of the same) and the
     # result is the fp32 start of the residual stream
     sinusoidal_base: Optional[float] = None
+    # the embedding leaves as the fp32 start of a residual stream whatever the table's dtype (implied by sinusoidal_base)
+    fp32_stream: bool = False

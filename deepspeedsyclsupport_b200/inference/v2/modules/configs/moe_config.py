@@ -18,6 +18,10 @@ class DSMoEConfig(DSModuleConfig):
     n_groups: int = 1
     keep_groups: int = 1
     use_correction: bool = False
+    # how a router logit becomes a score: "softmax" over the experts, or "sigmoid" of every logit on its own
+    score_function: str = "softmax"
+    # True: the chosen expert's score multiplies the expert's INPUT (out = sum_k expert_k(s_k h)) instead of its output
+    scale_input: bool = False
     # ActivationType.ClampedSwiGLU: min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + shift)
     act_alpha: float = 1.702
     act_limit: float = 7.0

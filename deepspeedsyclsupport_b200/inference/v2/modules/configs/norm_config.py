@@ -19,6 +19,8 @@ class DSNormConfig(DSModuleConfig):
     # "sandwich" blocks norm a sublayer's output before it is added to the residual: x += norm(branch) * (w_b + offset), and the
     # same pass produces the next sublayer's input norm(x) * (w + offset).  The residual stream is then kept in fp32.
     sandwich: bool = False
+    # sandwich blocks only: the normed branch is multiplied by this before it joins the stream (x += branch_mult * norm(branch) * ...)
+    branch_mult: float = 1.0
 
     @field_validator("channels")
     @classmethod

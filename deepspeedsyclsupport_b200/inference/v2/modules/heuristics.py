@@ -4,10 +4,11 @@ quantisation mode selects the fp8 tensor-core linear; everything else currently 
 from ..config_v2 import RaggedInferenceEngineConfig
 from ..inference_utils import ActivationType, NormTypeEnum
 from . import implementations  # noqa: F401  (registers the implementations)
-from .configs import DSLatentAttentionConfig, DSEmbeddingsConfig, DSLinearConfig, DSMoEConfig, DSNormConfig, DSSelfAttentionConfig, DSUnembedConfig
+from .configs import (DSDeltaRuleConfig, DSEmbeddingsConfig, DSLatentAttentionConfig, DSLinearConfig, DSMatrixMemoryConfig, DSMoEConfig, DSNormConfig,
+                      DSSelfAttentionConfig, DSUnembedConfig, DSWindowedAttentionConfig)
 from .interfaces import (DSEmbeddingBase, DSEmbeddingRegistry, DSLinearBase, DSLinearRegistry, DSMoEBase, DSMoERegistry, DSPostNormBase,
-                         DSPostNormRegistry, DSPreNormBase, DSPreNormRegistry, DSSelfAttentionBase, DSSelfAttentionRegistry, DSUnembedBase,
-                         DSUnembedRegistry)
+                         DSPostNormRegistry, DSPreNormBase, DSPreNormRegistry, DSRecurrentMixerBase, DSRecurrentRegistry, DSSelfAttentionBase,
+                         DSSelfAttentionRegistry, DSUnembedBase, DSUnembedRegistry)
 from .module_registry import ConfigBundle
 
 
@@ -19,11 +20,19 @@ def _quant_mode(engine_config) -> str:
 def instantiate_attention(attention_config, engine_config: RaggedInferenceEngineConfig = None) -> DSSelfAttentionBase:
     if isinstance(attention_config, DSLatentAttentionConfig):  # keys / values are up-projections of a cached latent
         return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name="latent_blocked_attention", config=attention_config))
+    if isinstance(attention_config, DSWindowedAttentionConfig):  # convolved q / k, values = keys, sliding window that keeps the first tokens
+        return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name="windowed_conv_attention", config=attention_config))
     return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name="dense_blocked_attention", config=attention_config))
 
 
+def instantiate_recurrent(mixer_config, engine_config: RaggedInferenceEngineConfig = None) -> DSRecurrentMixerBase:
+    """Token mixers with a fixed-size state per sequence; the config class names the recurrence."""
+    name = {DSMatrixMemoryConfig: "matrix_memory", DSDeltaRuleConfig: "channel_delta_rule"}[type(mixer_config)]
+    return DSRecurrentRegistry.instantiate_config(ConfigBundle(name=name, config=mixer_config))
+
+
 def instantiate_embed(embed_config: DSEmbeddingsConfig, engine_config: RaggedInferenceEngineConfig = None) -> DSEmbeddingBase:
-    name = "sinusoidal_embedding" if embed_config.sinusoidal_base is not None else "ragged_embedding"
+    name = "sinusoidal_embedding" if (embed_config.sinusoidal_base is not None or embed_config.fp32_stream) else "ragged_embedding"
     return DSEmbeddingRegistry.instantiate_config(ConfigBundle(name=name, config=embed_config))
 
 
@@ -40,7 +49,8 @@ def instantiate_linear(linear_config: DSLinearConfig, engine_config: RaggedInfer
 
 
 def instantiate_moe(moe_config: DSMoEConfig, engine_config: RaggedInferenceEngineConfig = None) -> DSMoEBase:
-    if moe_config.n_groups > 1 or moe_config.use_correction or ActivationType(moe_config.activation) == ActivationType.ClampedSwiGLU:
+    if (moe_config.n_groups > 1 or moe_config.use_correction or ActivationType(moe_config.activation) == ActivationType.ClampedSwiGLU or
+            moe_config.score_function != "softmax" or moe_config.scale_input):
         return DSMoERegistry.instantiate_config(ConfigBundle(name="grouped_topk_moe", config=moe_config))
     bundle = ConfigBundle(name="cutlass_multi_gemm_moe", config=moe_config, implementation_config={"weight_dtype": moe_config.input_dtype})
     return DSMoERegistry.instantiate_config(bundle)

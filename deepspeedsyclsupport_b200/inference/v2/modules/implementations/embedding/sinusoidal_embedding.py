@@ -1,4 +1,4 @@
-"""Token embedding plus a fixed sinusoidal position vector, written as the fp32 start of the residual stream.
+"""Token embedding, optionally plus a fixed sinusoidal position vector, written as the fp32 start of the residual stream.
 
 Entry 2i of the position vector is sin(p * base^(-2i / dim)) and entry 2i + 1 the cosine of the same angle, p being the token's
 position in its sequence.  The angles are formed in double precision on the device (a position in the thousands times a
@@ -25,7 +25,7 @@ class DSSinusoidalEmbedding(DSEmbeddingBase):
     def supports_config(config: DSEmbeddingsConfig) -> bool:
         if DtypeEnum(config.residual_dtype) not in (DtypeEnum.bf16, DtypeEnum.fp32):
             return False
-        return config.sinusoidal_base is not None and not config.positional_embedding and not config.use_token_type
+        return (config.sinusoidal_base is not None or config.fp32_stream) and not config.positional_embedding and not config.use_token_type
 
     def __init__(self, config: DSEmbeddingsConfig, implementation_config: Dict[str, Any] = None) -> None:
         super().__init__(config, implementation_config)
@@ -43,7 +43,7 @@ class DSSinusoidalEmbedding(DSEmbeddingBase):
     def forward(self, ragged_batch, word_embeddings: torch.Tensor, position_embeddings: Optional[torch.Tensor] = None,
                 token_type_ids: Optional[torch.Tensor] = None, token_type_embeddings: Optional[torch.Tensor] = None) -> torch.Tensor:
         assert position_embeddings is None and token_type_ids is None
-        if self._freq is None or self._freq.device != word_embeddings.device:
+        if self._config.sinusoidal_base is not None and (self._freq is None or self._freq.device != word_embeddings.device):
             self._freq = K.sinusoid_frequencies(self._config.embedding_dim, self._config.sinusoidal_base, word_embeddings.device)
         self._output = K.embed_sinusoid(ragged_batch.input_ids(), word_embeddings, ragged_batch.tok_pos(), self._freq)
         return self._output

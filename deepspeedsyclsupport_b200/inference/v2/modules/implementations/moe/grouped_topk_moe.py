@@ -1,9 +1,11 @@
-"""Mixture-of-experts MLP with a grouped, bias-corrected top-k router and a clamped gated activation.
+"""Mixture-of-experts MLP with a configurable fp32 router and a gated activation.
 
-Router (fp32): scores = softmax(W_r h) over all experts; the SELECTION uses scores + correction, restricted to the `keep_groups`
-contiguous expert groups whose best selection score is largest; the combine WEIGHTS are the plain scores of the chosen
-experts (optionally renormalised).  Experts: two grouped GEMMs over the rows sorted by expert with the gated activation
-between them; the weighted combine leaves in fp32 (it feeds an fp32 norm / residual).
+Router (fp32): scores = softmax(W_r h) over all experts, or (`score_function` "sigmoid") the sigmoid of every logit on its own; the
+SELECTION uses scores + correction (when the config has one), restricted to the `keep_groups` contiguous expert groups whose best
+selection score is largest; the WEIGHTS are the plain scores of the chosen experts (optionally renormalised).  They multiply the
+experts' outputs in the combine or, with `scale_input`, the experts' inputs in the scatter (out = sum_k expert_k(s_k h)).  Experts: two
+grouped GEMMs over the rows sorted by expert with the gated activation between them (clamped swish, or plain silu(g) * u for SiGLU); the
+combine leaves in fp32 (it feeds an fp32 norm / residual).
 
 The grouped GEMMs run on the persistent tcgen05 kernel (csrc/gemm/gemm_grouped.cu) when the operands are bf16 with
 TMA-compatible shapes, else on the CUDA-core grouped GEMM of csrc/ragged/latent_ops.cu (any shape, bf16 or true fp32)."""
@@ -30,7 +32,7 @@ class DSGroupedTopKMoE(DSMoEBase):
     def supports_config(config: DSMoEConfig) -> bool:
         if config.input_dtype != config.output_dtype or DtypeEnum(config.input_dtype) not in (DtypeEnum.bf16, DtypeEnum.fp32):
             return False
-        if ActivationType(config.activation) != ActivationType.ClampedSwiGLU:
+        if ActivationType(config.activation) not in (ActivationType.ClampedSwiGLU, ActivationType.SiGLU) or config.score_function not in ("softmax", "sigmoid"):
             return False
         g, k = config.n_groups, config.keep_groups
         return (1 <= config.top_k <= min(config.n_experts, 32) and config.n_experts <= 2048 and g >= 1 and config.n_experts % g == 0 and
@@ -68,10 +70,14 @@ class DSGroupedTopKMoE(DSMoEBase):
         assert mlp_1_b is None and mlp_2_b is None, "these experts have no biases"
         assert (correction is not None) == c.use_correction
         logits = dense_matmul(router_input if router_input is not None else hidden_states.float(), gate_w)  # fp32 router logits
-        counts, scores, assignments, offsets = K.grouped_topk_gating(logits, c.top_k, correction, c.n_groups, c.keep_groups, c.normalize_scores)
-        moe_in, cumsum, slots = K.moe_scatter_rows(hidden_states, counts, assignments, offsets)
+        counts, scores, assignments, offsets = K.grouped_topk_gating(logits, c.top_k, correction, c.n_groups, c.keep_groups, c.normalize_scores,
+                                                                     sigmoid_scores=c.score_function == "sigmoid")
+        moe_in, cumsum, slots = K.moe_scatter_rows(hidden_states, counts, assignments, offsets, row_scale=scores if c.scale_input else None)
         gu = self._grouped(moe_in, mlp_1_w, cumsum)
-        act = K.clamped_swish_gate(gu, c.act_alpha, c.act_limit, c.act_shift)
+        if ActivationType(c.activation) == ActivationType.SiGLU:  # silu(g) * u: the clamped form without its limit and shift
+            act = K.clamped_swish_gate(gu, 1.0, float("inf"), 0.0)
+        else:
+            act = K.clamped_swish_gate(gu, c.act_alpha, c.act_limit, c.act_shift)
         out = self._grouped(act, mlp_2_w, cumsum)
-        self._output = K.moe_gather_rows(out, scores, slots)
+        self._output = K.moe_gather_rows(out, None if c.scale_input else scores, slots)
         return self._output

@@ -40,12 +40,14 @@ class RaggedBatchWrapper:
         self._h_tok_pos = host(self.max_tokens, torch.int32)
         self._h_last = host(self.max_seqs, torch.int32)
         self._h_rows = host(self.max_tokens, torch.int32)
+        self._h_seq_desc = host((self.max_seqs, 4), torch.int32)  # per sequence: first row, new tokens, tokens seen before, state slot
         self.max_blocks_per_seq = -(-config.max_context // 1)  # set by the state manager
         self._d_ids = torch.zeros(self.max_tokens, dtype=torch.int64, device=dev)
         self._d_tok_seq = torch.zeros(self.max_tokens, dtype=torch.int32, device=dev)
         self._d_tok_pos = torch.zeros(self.max_tokens, dtype=torch.int32, device=dev)
         self._d_last = torch.zeros(self.max_seqs, dtype=torch.int32, device=dev)
         self._d_rows = torch.zeros(self.max_tokens, dtype=torch.int32, device=dev)
+        self._d_seq_desc = torch.zeros(self.max_seqs, 4, dtype=torch.int32, device=dev)
         self._h_block_table = None
         self._d_block_table = None
         self._copied = None  # CUDA event behind the last batch's host -> device copies
@@ -93,6 +95,8 @@ class RaggedBatchWrapper:
         self._h_ids[self._n_tokens:self._n_tokens + n].copy_(tokens.to(torch.int64))
         blocks = seq_descriptor.kv_block_ids()
         self._h_block_table[self._n_seqs, :blocks.numel()].copy_(blocks)
+        d = self._h_seq_desc[self._n_seqs]
+        d[0], d[1], d[2], d[3] = self._n_tokens, n, seq_descriptor.seen_tokens, getattr(seq_descriptor, "state_slot", -1)
         self._seq_start.append(self._n_tokens)
         self._seq_ntok.append(n)
         self._seq_seen.append(seq_descriptor.seen_tokens)
@@ -112,6 +116,7 @@ class RaggedBatchWrapper:
         if self._n_rows:
             self._d_rows[:self._n_rows].copy_(self._h_rows[:self._n_rows], non_blocking=True)
         self._d_block_table[:self._n_seqs].copy_(self._h_block_table[:self._n_seqs], non_blocking=True)
+        self._d_seq_desc[:self._n_seqs].copy_(self._h_seq_desc[:self._n_seqs], non_blocking=True)
         if self._d_ids.is_cuda:
             self._copied = torch.cuda.Event()
             self._copied.record()
@@ -139,6 +144,10 @@ class RaggedBatchWrapper:
 
     def block_table(self):
         return self._d_block_table
+
+    def seq_desc(self):
+        """[n_seqs, 4] int32 on the device: (first row of the sequence in the batch, new tokens, tokens seen before, state slot)."""
+        return self._d_seq_desc[:self._n_seqs]
 
     def atoms(self, q_block=128, kv_block=128):
         return build_atoms(self._seq_start, self._seq_ntok, self._seq_seen, q_block, kv_block)

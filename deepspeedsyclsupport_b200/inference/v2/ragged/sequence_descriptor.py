@@ -4,8 +4,9 @@ import torch
 
 class DSSequenceDescriptor:
 
-    def __init__(self, tracking_id, max_blocks, block_size):
+    def __init__(self, tracking_id, max_blocks, block_size, state_slot=-1):
         self._tracking_id = tracking_id
+        self._state_slot = state_slot  # slot of the sequence's fixed-size state (models with recurrent mixers), -1: none
         self._seen_tokens = 0
         self._in_flight_tokens = 0
         self._block_size = block_size
@@ -15,6 +16,10 @@ class DSSequenceDescriptor:
     @property
     def seen_tokens(self):
         return self._seen_tokens
+
+    @property
+    def state_slot(self):
+        return self._state_slot
 
     @property
     def in_flight_tokens(self):

@@ -368,15 +368,17 @@ int dsb200_fp8_rowwise_quantize(const void* x, void* q, float* scales, int rows,
 
 /* ---- csrc/ragged/latent_ops.cu */
 /* out[t, :] = table[ids[t], :] + sinusoid(tok_pos[t]): entry 2i = sin(p f_i), entry 2i + 1 = cos(p f_i); `freq` holds the
- * ceil(dim / 2) frequencies as doubles on the device.  table_dtype: 0 = bf16, 1 = fp32.  out is fp32. */
+ * ceil(dim / 2) frequencies as doubles on the device, or is null for no position vector (tok_pos is then unused).
+ * table_dtype: 0 = bf16, 1 = fp32.  out is fp32. */
 int dsb200_embed_sinusoid(const long long* ids, const void* table, int table_dtype, const int* tok_pos, const double* freq,
                           float* out, int n_tokens, int dim, dsb200_stream_t stream);
-/* Per row of the fp32 residual x [n_rows, dim] (row rows[r] when `rows` is given): if y: x += rms_norm(y) * (wb + ob); if w:
- * out = rms_norm(x) * (w + o).  y and out are bf16 (dtype 0) or fp32 (dtype 1); the weights are fp32.  out32 (optional, fp32
- * [n_rows, dim]) receives the normed values before their rounding to out's dtype (a router that decides in fp32 reads these). */
-int dsb200_sandwich_norm(float* x, const void* y, int y_dtype, const float* wb, float ob, const float* w, float o,
-                         void* out, int out_dtype, float* out32, const int* rows, int n_rows, int dim, float eps,
-                         dsb200_stream_t stream);
+/* Per row of the fp32 residual x [n_rows, dim] (row rows[r] when `rows` is given): if y: x += y_mult * rms_norm(y) * (wb + ob); if w:
+ * out = rms_norm(x) * (w + o); if plain_out (and no w): out = x.  y and out are bf16 (dtype 0) or fp32 (dtype 1); the weights are fp32.
+ * out32 (optional, fp32 [n_rows, dim]) receives the normed values before their rounding to out's dtype (a router that decides in fp32
+ * reads these). */
+int dsb200_sandwich_norm(float* x, const void* y, int y_dtype, const float* wb, float ob, float y_mult, const float* w,
+                         float o, void* out, int out_dtype, float* out32, const int* rows, int n_rows, int dim, float eps,
+                         int plain_out, dsb200_stream_t stream);
 /* lat [n_tokens, ld] holds (query latent [nq] | key/value latent [nkv]) of every token.  cq [n_tokens, nq] = plain-weight RMS norm
  * of the first part; the RMS-normed second part is written to the token's row of cache [blocks, block_size, cache_ld] (cache_ld >= nkv:
  * rows may be padded to a width the tensor-core attention takes; the padding is never written). */
@@ -405,19 +407,21 @@ int dsb200_clamped_swish_gate(const void* gu, void* out, long long rows, int F, 
                               int dtype, dsb200_stream_t stream);
 /* x[r, c] = cap * tanh(x[r, c] / cap) over fp32 [rows, cols] with row stride ld */
 int dsb200_softcap(float* x, long long ld, long long rows, int cols, float cap, dsb200_stream_t stream);
-/* Router: softmax over the E logits of a token; selection score = score + correction[e] (correction may be null); experts are split
+/* Router: scores = softmax over the E logits of a token, or (sigmoid_scores) the sigmoid of every logit on its own; selection score =
+ * score + correction[e] (correction may be null); experts are split
  * into `groups` contiguous groups of equal size, of which the `keep` with the largest maximal selection score stay selectable; the top_k
  * selectable experts by selection score are assigned; their weights are the uncorrected scores (divided by their sum when
  * `normalize`).  Outputs as dsb200_top_k_gating; expert_counts must be zeroed by the caller. */
 int dsb200_grouped_topk_gating(const float* logits, const float* correction, int* expert_counts, float* scores,
                                int* assignments, int* offsets, int n_tokens, int n_experts, int top_k, int groups,
-                               int keep, int normalize, dsb200_stream_t stream);
+                               int keep, int normalize, int sigmoid_scores, dsb200_stream_t stream);
 /* Rows of x [n_tokens, dim] copied into expert-sorted order (any dim; dtype 0 = bf16, 1 = fp32); also writes the inclusive
- * per-expert row cumsum and every (token, k)'s row. */
+ * per-expert row cumsum and every (token, k)'s row.  row_scale (optional, fp32 [n_tokens, top_k]): copy k of token t is multiplied by
+ * row_scale[t, k] (routers whose weight applies to the expert's input). */
 int dsb200_moe_scatter_rows(const void* x, const int* expert_counts, const int* assignments, const int* offsets,
                             long long* expert_cumsum, void* moe_in, int* mapped_slots, int n_tokens, int n_experts,
-                            int dim, int top_k, int dtype, dsb200_stream_t stream);
-/* out[t, :] (fp32) = sum_k scores[t, k] * moe_out[mapped_slots[t, k], :] */
+                            int dim, int top_k, int dtype, const float* row_scale, dsb200_stream_t stream);
+/* out[t, :] (fp32) = sum_k scores[t, k] * moe_out[mapped_slots[t, k], :]; scores may be null (plain sum) */
 int dsb200_moe_gather_rows(const void* moe_out, const float* scores, const int* mapped_slots, float* out, int n_tokens,
                            int dim, int top_k, int dtype, dsb200_stream_t stream);
 /* Grouped expert GEMM on CUDA cores: out[r, :] = w[expert(r)] x[r, :] for the R rows sorted by expert; x [R, K], w [E, N, K],
@@ -443,6 +447,66 @@ int dsb200_moe_scatter(const void* x, const int* expert_counts, const int* assig
                        int top_k, dsb200_stream_t stream);
 int dsb200_moe_gather(const void* moe_out, const float* scores, const int* mapped_slots, void* out, int n_tokens, int dim,
                       int top_k, dsb200_stream_t stream);
+
+/* ---- csrc/ragged/recurrent_ops.cu */
+/* Floats of state_S per (slot, head) for a d x dv recurrent state (the layout is the scan kernels' own). */
+long long dsb200_scan_state_floats(int d, int dv);
+/* proj [T, ld] (dtype 0 = bf16, 1 = fp32) holds, per token, the projections a windowed attention mixer convolves: queries [H d] at
+ * column q_col0 and keys [G d] at k_col0.  Per token: short convolution (weights fp32 [channels, taps], last column = current token,
+ * earlier rows from the batch or from `state` [slots, taps - 1, (H + G) d]) -> the convolved keys go to plane 1 of the token's cache row
+ * (they are the values); RMS norm over the whole q / whole k projection with plain weights norm_q / norm_k; rotation of pairs (2i, 2i + 1)
+ * of the first rot_dims entries of every head by pos * freq[i] (freq: doubles on the device); q to q_out [T, q_ld], k to cache plane 0.
+ * cache [blocks, 2, block_size, G, d].  Call dsb200_conv_state_update afterwards. */
+int dsb200_window_qk_prepare(const void* proj, long long ld, int q_col0, int k_col0, const float* conv_q,
+                             const float* conv_k, const float* norm_q, const float* norm_k, const void* state,
+                             const int* seq_desc, const int* tok_seq, const int* tok_pos, const int* block_table,
+                             int bt_stride, int block_size, void* cache, void* q_out, long long q_ld, const double* freq,
+                             int n_tokens, int H, int G, int d, int taps, int rot_dims, float eps, int dtype,
+                             dsb200_stream_t stream);
+/* Columns st_col0 .. st_col0 + C of state [slots, taps - 1, st_ld] <- the last taps - 1 projected rows (columns col0 .. col0 + C of proj
+ * [T, ld]) of every sequence of the batch, older rows shifting up when the step brought fewer than taps - 1 tokens.  Run after the
+ * kernels that read the state. */
+int dsb200_conv_state_update(const void* proj, long long ld, int col0, void* state, int st_ld, int st_col0,
+                             const int* seq_desc, int n_seqs, int C, int taps, int dtype, dsb200_stream_t stream);
+/* out[t, h d + c] = out_scale * sum_j softmax_j(scale q_h . k_j) v_j[c] over the keys j <= pos(t) of the token's sequence with
+ * pos - j < window or j < keep_first.  q [T, q_ld] (H heads of d), cache [blocks, 2, block_size, G, d] (plane 0 keys, 1 values), query head
+ * h reads key/value head h / (H / G); out [T, out_ld].  CUDA cores, fp32 scores and accumulation, any sizes; dtype 0 = bf16, 1 = fp32. */
+int dsb200_window_attention(const void* q, long long q_ld, const void* cache, const int* tok_seq, const int* tok_pos,
+                            const int* block_table, int bt_stride, int block_size, void* out, long long out_ld,
+                            int n_tokens, int H, int G, int d, int window, int keep_first, float scale, float out_scale,
+                            int dtype, dsb200_stream_t stream);
+/* Matrix memory with exponential gating, per sequence and head, over the new tokens in order:
+ *   i = cap tanh((gates[t, h] + bias_i[h]) / cap),  f = logsigmoid(cap tanh((gates[t, H + h] + bias_f[h]) / cap)),
+ *   m' = max(f + m, i);  S <- exp(f + m - m') S + exp(i - m') k v^T;  n likewise with k;  out = S^T q / (max(|n . q|, exp(-m')) + 1e-6)
+ * with q = proj[q_col0 ..] * d^-1/2, k, v from proj [T, ld] (dtype 0 = bf16, 1 = fp32); gates fp32 [T, 2 H]; out fp32 [T, H dv].
+ * state_S [slots, H, dsb200_scan_state_floats(d, dv)], state_n [slots, H, d], state_m [slots, H], all fp32; a sequence at position 0 starts
+ * from zeros (m = 0). */
+int dsb200_matrix_memory_scan(const void* proj, long long ld, int q_col0, int k_col0, int v_col0, const float* gates,
+                              const float* bias_i, const float* bias_f, float cap, const int* seq_desc, float* state_S,
+                              float* state_n, float* state_m, float* out, int n_seqs, int H, int d, int dv, int dtype,
+                              dsb200_stream_t stream);
+/* Inputs of the delta-rule scan from the fused projection proj [T, ld] (dtype 0 = bf16, 1 = fp32): q [G d] at q_col0, k [G d] at k_col0, v
+ * [H dv] at v_col0, each through its short convolution (weights fp32 [channels, taps]; earlier rows from the batch or from `state`
+ * [slots, taps - 1, 2 G d + H dv]) and silu; q and k then scaled to unit length per head (x / sqrt(sum x^2 + 1e-6)), q also by d^-1/2.
+ * qn, kn fp32 [T, G d]; vo fp32 [T, H dv].  Call dsb200_conv_state_update (three column ranges) afterwards. */
+int dsb200_delta_prepare(const void* proj, long long ld, int q_col0, int k_col0, int v_col0, const float* conv_q,
+                         const float* conv_k, const float* conv_v, const void* state, const int* seq_desc,
+                         const int* tok_seq, float* qn, float* kn, float* vo, int n_tokens, int G, int H, int d, int dv,
+                         int taps, int dtype, dsb200_stream_t stream);
+/* Gated delta rule with one decay per head and key channel, per sequence and head over the new tokens in order:
+ *   g = exp(-exp(A_log[h]) softplus(a_pre[t, h, :] + dt_bias[h, :]));  S <- diag(g) S;  u = sigmoid(beta_pre[t, h]) (v - S^T k);
+ *   S <- S + k u^T;  out = S^T q
+ * qn, kn fp32 [T, G d] (head h reads q / k head h / (H / G)), v fp32 [T, H dv], beta_pre fp32 [T, H], a_pre fp32 [T, H d]; out fp32 [T, H dv];
+ * state_S [slots, H, dsb200_scan_state_floats(d, dv)] fp32; a sequence at position 0 starts from zeros. */
+int dsb200_delta_rule_scan(const float* qn, const float* kn, const float* v, const float* beta_pre, const float* a_pre,
+                           const float* A_log, const float* dt_bias, const int* seq_desc, float* state_S, float* out,
+                           int n_seqs, int H, int G, int d, int dv, dsb200_stream_t stream);
+/* out[t, h dv + c] = o[t, h, c] / sqrt(mean_c o[t, h, :]^2 + eps) * w[h * w_stride + c] * sigmoid(gate[t, h dv + c]) * mult.  o fp32
+ * [T, H dv]; w fp32 (w_stride = dv: one weight row per head, 0: one row shared by the heads); gate [T, gate_ld] and out [T, out_ld] in the
+ * activation dtype (0 = bf16, 1 = fp32). */
+int dsb200_head_norm_gate(const float* o, const float* w, int w_stride, const void* gate, long long gate_ld, void* out,
+                          long long out_ld, int n_tokens, int H, int dv, float eps, float mult, int dtype,
+                          dsb200_stream_t stream);
 
 /* ---- csrc/random_ltd/token_ops.cu */
 /* idx: int32 [rows, reserved] of unique positions in [0, seq); sorted ascending in place, row by row. */
