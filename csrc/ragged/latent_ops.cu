@@ -71,13 +71,13 @@ __global__ void embed_sinusoid_kernel(const long long* __restrict__ ids, const T
                                       const double* __restrict__ freq, float* __restrict__ out, int dim) {
   const int t = blockIdx.x;
   const long long id = ids[t];
-  const double p = static_cast<double>(tok_pos[t]);
   const TW* row = table + id * dim;
   float* o = out + static_cast<size_t>(t) * dim;
-  if (freq == nullptr) {  // no position vector: the table row alone starts the stream
+  if (freq == nullptr) {  // no position vector: the table row alone starts the stream (tok_pos may be null)
     for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = to_f(row[i]);
     return;
   }
+  const double p = static_cast<double>(tok_pos[t]);
   for (int i = threadIdx.x; 2 * i < dim; i += blockDim.x) {
     double s, c;
     sincos(p * freq[i], &s, &c);

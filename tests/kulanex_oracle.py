@@ -291,3 +291,36 @@ def moe(experts=4, top=2, ff=16):
 
 def make_config(layers, vocab=96, width=48, eps=1e-5, residual_mult=0.5):
     return {"architecture": "Kulanex", "layers": layers, "norm": {"eps": eps}, "residual_mult": residual_mult, "vocab": vocab, "width": width}
+
+
+def greedy(cfg, w, prompt, n_new):
+    """Greedy continuation, recomputing the whole sequence for every new token."""
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(forward(cfg, w, toks)[-1].argmax())
+        out.append(nxt)
+        toks.append(nxt)
+    return out
+
+
+def write_model(folder, cfg, w):
+    """config.json + model.safetensors (8-byte little-endian header length, JSON header, raw little-endian data) -> folder."""
+    import json
+    import os
+    import struct
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    names = {torch.bfloat16: "BF16", torch.float32: "F32", torch.int32: "I32"}
+    header, blobs, at = {}, [], 0
+    for k, t in w.items():
+        t = t.contiguous()
+        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        header[k] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    hj = json.dumps(header).encode()
+    hj += b" " * (-len(hj) % 8)
+    with open(os.path.join(folder, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(hj)) + hj + b"".join(blobs))
+    return folder
