@@ -519,4 +519,228 @@ def run_linasun(args):
           flush=True)
 
 
-WORKLOADS = {"fastgen70b": run_fastgen70b, "mixtral": run_mixtral, "ulysses13b": run_ulysses13b, "linasun": run_linasun}
+# ---- Kulanex beside a Mixtral of equal size
+KULANEX_SIZES = {  # width, layers, attention heads, head_dim, kv heads, window, experts, top, ff, vocab
+    "s": (2048, 4, 16, 128, 4, 1024, 8, 2, 1024, 32000),
+    "m": (4096, 4, 32, 128, 8, 1024, 8, 2, 2048, 32000),
+}
+
+
+def _kulanex_state(torch, dev, W, L, H, d, hkv, window, E, top, ff, V):
+    """Layers alternate 'parallel' (windowed attention H:hkv x d beside a matrix memory of H/2 heads, 64 x 2d) and 'channel_delta'
+    (H heads, d x d), all with the MoE feed-forward; the layer input projections add up to about the twin's."""
+    mh, md, mv, lr = H // 2, 64, 2 * d, 128
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": E, "top": top}}
+    par = {"type": "parallel", "mlp": moe,
+           "mixer": {"left": {"conv": 4, "dim": d, "heads": H, "kv_heads": hkv, "mask": {"keep_first": 4, "size": window},
+                              "rot": {"base": 1e6, "dims": d // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}, "scale": d ** -0.5, "vdim": d},
+                     "left_scale": 1.0, "right": {"dim": md, "gate_cap": 15.0, "heads": mh, "vdim": mv}, "right_scale": 1.0}}
+    dl = {"type": "channel_delta", "mlp": moe, "mixer": {"conv": 4, "dim": d, "heads": H, "kv_heads": H, "vdim": d}}
+    cfg = {"architecture": "Kulanex", "vocab": V, "width": W, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "layers": [par if i % 2 == 0 else dl for i in range(L)]}
+
+    def r(*shape, std=0.02, mean=0.0):
+        return torch.empty(*shape, device=dev, dtype=torch.bfloat16).normal_(mean, std)
+
+    sd = {"embed": r(V, W, std=1.0), "final.norm": r(W), "head": r(V, W)}
+    for i in range(L):
+        p = f"l{i}."
+        sd.update({p + "norm1": r(W), p + "norm2": r(W), p + "mlp.router": r(E, W, std=0.5)})
+        for e in range(E):
+            sd.update({p + f"mlp.e{e}.gate": r(ff, W), p + f"mlp.e{e}.up": r(ff, W), p + f"mlp.e{e}.down": r(W, ff)})
+        if i % 2 == 0:
+            a, b = p + "mix.left.", p + "mix.right."
+            sd.update({a + "q": r(H * d, W), a + "k": r(hkv * d, W), a + "q.conv": r(H * d, 4, std=0.5), a + "k.conv": r(hkv * d, 4, std=0.5),
+                       a + "q.norm": r(H * d, mean=1.0), a + "k.norm": r(hkv * d, mean=1.0), a + "o": r(W, H * d),
+                       b + "q": r(mh * md, W), b + "k": r(mh * md, W), b + "v": r(mh * mv, W), b + "g": r(mh * mv, W), b + "o": r(W, mh * mv),
+                       b + "norm": r(mh * mv, mean=1.0), b + "i": r(mh, W), b + "i.b": r(mh), b + "f": r(mh, W), b + "f.b": r(mh, mean=3.0)})
+        else:
+            a = p + "mix."
+            sd.update({a + "q": r(H * d, W), a + "k": r(H * d, W), a + "v": r(H * d, W), a + "q.conv": r(H * d, 4, std=0.5), a + "k.conv": r(H * d, 4, std=0.5),
+                       a + "v.conv": r(H * d, 4, std=0.5), a + "b": r(H, W), a + "A_log": r(H, mean=-2.5), a + "norm": r(d, mean=1.0), a + "a1": r(lr, W),
+                       a + "a2": r(H * d, lr), a + "dt_bias": r(H * d, mean=-2.0), a + "g1": r(lr, W), a + "g2": r(H * d, lr), a + "o": r(W, H * d)})
+    return cfg, sd
+
+
+def _kulanex_kernel_table(torch, peaks, W, H, d, hkv, window, E, top, ff, T, ctx, n_dec):
+    """Every kernel of the design beside the like kernel of the Mixtral path, isolated, with the fraction of the measured roofline (HBM copy
+    bandwidth for the streaming kernels, cuBLAS bf16 rate for attention prefill).  The recurrent scans have no like among the attention
+    models' kernels but the attention itself; they are listed beside it with their own bytes (inputs + outputs + the state once in, once out)."""
+    from deepspeedsyclsupport_b200.inference.v2 import kernels as K
+    from deepspeedsyclsupport_b200.ops import fused_ops as FO
+    dev = torch.device("cuda")
+    bf = torch.bfloat16
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=dev)
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    rows = []
+
+    def add(name, ms, like, like_ms, nbytes=None, like_bytes=None, flops=None, like_flops=None):
+        def frac(ms_, b, f):
+            return round(max((b or 0) / hbm, (f or 0) / tf) / (ms_ * 1e-3), 3)
+        rows.append({"kernel": name, "ms": round(ms, 4), "roofline_frac": frac(ms, nbytes, flops), "like": like, "like_ms": round(like_ms, 4),
+                     "like_roofline_frac": frac(like_ms, like_bytes if like_bytes is not None else nbytes, like_flops if like_flops is not None else flops)})
+
+    x32, y, g32 = torch.randn(T, W, device=dev), torch.randn(T, W, device=dev).to(bf), torch.randn(W, device=dev)
+    xb, gb = torch.randn(T, W, device=dev).to(bf), torch.randn(W, device=dev).to(bf)
+    add("post-norm into the fp32 stream + bf16 copy", _event_ms(torch, lambda: K.sandwich_norm(x32, y, g32, 1.0, None, 0.0, 1e-6, y_mult=0.5, plain_out=True), 20, flush),
+        "rms_norm + residual add (bf16 stream)", _event_ms(torch, lambda: FO.rms_norm(y, gb, 1e-5, xb), 20, flush),
+        nbytes=T * W * (4 + 4 + 2 + 2), like_bytes=T * W * (2 + 2 + 2 + 2))
+    lg = torch.randn(T, E, device=dev)
+    add("grouped_topk_gating (sigmoid scores)", _event_ms(torch, lambda: K.grouped_topk_gating(lg, top, sigmoid_scores=True), 20, flush),
+        "top_k_gating", _event_ms(torch, lambda: K.top_k_gating(lg, top), 20, flush), nbytes=T * (E * 4 + top * 12))
+    counts, scores, asg, off = K.top_k_gating(lg, top)
+    h = torch.randn(T, W, device=dev).to(bf)
+    add("moe_scatter_rows (scaled copies)", _event_ms(torch, lambda: K.moe_scatter_rows(h, counts, asg, off, row_scale=scores), 20, flush),
+        "moe_scatter", _event_ms(torch, lambda: K.moe_scatter(h, counts, asg, off), 20, flush), nbytes=T * W * 2 * (1 + top))
+    moe_in, cumsum, slots = K.moe_scatter(h, counts, asg, off)
+    dn = torch.randn(T * top, W, device=dev).to(bf)
+    add("moe_gather_rows (plain sum, fp32 out)", _event_ms(torch, lambda: K.moe_gather_rows(dn, None, slots), 20, flush),
+        "moe_gather (bf16 out)", _event_ms(torch, lambda: K.moe_gather(dn, scores, slots), 20, flush),
+        nbytes=T * W * (2 * top + 4), like_bytes=T * W * (2 * top + 2))
+    # token mixers: one prompt portion per sequence after ctx cached tokens; then n_dec decode tokens at context ctx
+    bs = 128
+    mh, md, mv = H // 2, 64, 2 * d
+    from deepspeedsyclsupport_b200.inference.v2.modules.implementations.attention.windowed_conv_attention import scaled_rotary_frequencies
+    freq = scaled_rotary_frequencies(d // 2, 1e6, None).to(dev)
+    inv_freq = (1e6 ** (-torch.arange(0, d, 2, device=dev, dtype=torch.float32) / d))
+    for label, n_seq, new, seen in (("prefill", max(1, T // 2048), min(T, 2048), ctx), ("decode", n_dec, 1, ctx)):
+        per = -(-(seen + new) // bs)
+        nb = n_seq * per
+        bt = torch.arange(nb, dtype=torch.int32, device=dev).view(n_seq, per)
+        tok_seq = torch.arange(n_seq, dtype=torch.int32, device=dev).repeat_interleave(new)
+        tok_pos = (seen + torch.arange(new, dtype=torch.int32, device=dev)).repeat(n_seq)
+        desc = torch.tensor([[i * new, new, seen, i] for i in range(n_seq)], dtype=torch.int32, device=dev)
+        Tn = n_seq * new
+        dec = label == "decode"
+        kv = torch.randn(nb, 2, bs, hkv, d, device=dev).to(bf)
+        qkv = torch.randn(Tn, (H + 2 * hkv) * d, device=dev).to(bf)
+        # q / k preparation (convolution, norms, rotation, append) vs rotary + append
+        C = (H + hkv) * d
+        proj = torch.randn(Tn, C, device=dev).to(bf)
+        cw, nw = torch.randn(C, 4, device=dev), torch.randn(C, device=dev)
+        cstate = torch.zeros(n_seq, 3, C, device=dev, dtype=bf)
+        qo = torch.empty(Tn, H * d, device=dev, dtype=bf)
+
+        def prep():
+            K.window_qk_prepare(proj, 0, H * d, cw, cw[H * d:], nw, nw[H * d:], cstate, desc, tok_seq, tok_pos, bt, kv, qo, freq, H, hkv, d, 4, d // 2, 1e-6)
+            K.conv_state_update(proj, 0, C, cstate, 0, desc, n_seq, 4)
+        add(f"window_qk_prepare + conv_state_update, {label}", _event_ms(torch, prep, 10, flush),
+            f"kv_rotary_append, {label}", _event_ms(torch, lambda: K.kv_rotary_append(qkv, kv, tok_seq, tok_pos, bt, inv_freq, H, hkv, d), 10, flush),
+            nbytes=Tn * (C * 2 + H * d * 2 + 2 * hkv * d * 2), like_bytes=Tn * ((H + 2 * hkv) * d * 2 * 2 - H * d * 0 + 0))
+        vis = min(window, seen + new)  # keys a query sees (about)
+        keys = n_seq * new * vis
+        out = torch.empty(Tn, H * d, device=dev, dtype=bf)
+        from deepspeedsyclsupport_b200.inference.v2.modules.implementations.attention.windowed_conv_attention import windowed_attention
+        add(f"windowed attention with kept tokens, {label}", _event_ms(torch, lambda: windowed_attention(qo, kv, tok_seq, tok_pos, bt, out, H, hkv, d, window, 4, d ** -0.5, 1.0, decode=dec), 10, flush),
+            f"paged flash attention, window {window}, {label} (GQA {H}:{hkv})",
+            _event_ms(torch, lambda: K.paged_attention(qkv, kv, tok_seq, tok_pos, bt, H, hkv, d, d ** -0.5, decode=dec, window=window), 10, flush),
+            nbytes=n_seq * min(seen + new, window + new) * hkv * d * 4 + Tn * H * d * 4, flops=4.0 * keys * H * d)
+        # recurrent scans
+        like_ms, like_frac_b = rows[-1]["like_ms"], n_seq * min(seen + new, window + new) * hkv * d * 4 + Tn * H * d * 4
+        pm = torch.randn(Tn, mh * (2 * md + 2 * mv), device=dev).to(bf) * 0.1
+        gates = torch.randn(Tn, 2 * mh, device=dev)
+        bi, bfg = torch.zeros(mh, device=dev), torch.full((mh, ), 3.0, device=dev)
+        sS = torch.zeros(n_seq, mh, K.scan_state_floats(md, mv), device=dev)
+        sn, smx = torch.zeros(n_seq, mh, md, device=dev), torch.zeros(n_seq, mh, device=dev)
+        state_b = n_seq * mh * md * mv * 4 * 2
+        add(f"matrix_memory_scan ({mh} x {md} x {mv}), {label}",
+            _event_ms(torch, lambda: K.matrix_memory_scan(pm, 0, mh * md, 2 * mh * md, gates, bi, bfg, 15.0, desc, n_seq, sS, sn, smx, mh, md, mv), 5, flush),
+            f"paged flash attention, {label}", like_ms, nbytes=Tn * mh * (2 * md + mv) * 2 + Tn * mh * mv * 4 + state_b, like_bytes=like_frac_b,
+            flops=0, like_flops=4.0 * keys * H * d)
+        qn, kn, vv = torch.randn(Tn, H * d, device=dev) * 0.1, torch.randn(Tn, H * d, device=dev) * 0.1, torch.randn(Tn, H * d, device=dev)
+        bp, ap = torch.randn(Tn, H, device=dev), torch.randn(Tn, H * d, device=dev)
+        Al, dtb = torch.full((H, ), -2.5, device=dev), torch.full((H * d, ), -2.0, device=dev)
+        dS = torch.zeros(n_seq, H, K.scan_state_floats(d, d), device=dev)
+        add(f"delta_rule_scan ({H} x {d} x {d}), {label}", _event_ms(torch, lambda: K.delta_rule_scan(qn, kn, vv, bp, ap, Al, dtb, desc, n_seq, dS, H, H, d, d), 5, flush),
+            f"paged flash attention, {label}", like_ms, nbytes=Tn * H * (4 * d * 4 + 4) + Tn * H * d * 4 + n_seq * H * d * d * 8, like_bytes=like_frac_b,
+            flops=0, like_flops=4.0 * keys * H * d)
+        p3 = torch.randn(Tn, 3 * H * d, device=dev).to(bf)
+        c3 = torch.randn(3 * H * d, 4, device=dev)
+        st3 = torch.zeros(n_seq, 3, 3 * H * d, device=dev, dtype=bf)
+
+        def dprep():
+            K.delta_prepare(p3, 0, H * d, 2 * H * d, c3, c3[H * d:], c3[2 * H * d:], st3, desc, tok_seq, H, H, d, d, 4)
+            K.conv_state_update(p3, 0, 3 * H * d, st3, 0, desc, n_seq, 4)
+        add(f"delta_prepare + conv_state_update, {label}", _event_ms(torch, dprep, 10, flush), f"kv_rotary_append, {label}", rows[-4]["like_ms"],
+            nbytes=Tn * 3 * H * d * (2 + 4), like_bytes=Tn * (H + 2 * hkv) * d * 4)
+        o32, gt, og = torch.randn(Tn, H * d, device=dev), torch.randn(Tn, H * d, device=dev).to(bf), torch.empty(Tn, H * d, device=dev, dtype=bf)
+        add(f"head_norm_gate, {label}", _event_ms(torch, lambda: K.head_norm_gate(o32, nw[:d].contiguous(), gt, og, H, d, 1e-6, shared_weight=True), 10, flush),
+            "gated_act (silu)", _event_ms(torch, lambda: FO.gated_act(torch.cat([gt, gt], 1) if False else qkv[:, :2 * (H * d // 2)].contiguous(), "silu"), 10, flush),
+            nbytes=Tn * H * d * 8, like_bytes=Tn * H * d * 3)
+    return rows
+
+
+def run_kulanex(args):
+    """Prefill and decode throughput of Kulanex through the FastGen engine at a few layer sizes, beside a Mixtral of equal size (same
+    width, layers, heads, experts, ff, top-k, vocabulary), plus the isolated kernels of the design beside their likes."""
+    sys.path.insert(0, ROOT)
+    import torch
+    import deepspeedsyclsupport_b200 as deepspeed
+    from deepspeedsyclsupport_b200 import comm as dist
+    from deepspeedsyclsupport_b200.inference.v2 import RaggedInferenceEngineConfig, build_engine_from_state_dict
+    from deepspeedsyclsupport_b200.ops import native
+    deepspeed.init_distributed()
+    assert dist.get_world_size() == 1, "--workload kulanex is a one-GPU comparison"
+    dev = torch.device("cuda", torch.cuda.current_device())
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")):
+        peaks = dict(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))), source="measured")
+    n_seqs, prompt, budget = min(args.sequences, 64), 1024, 4096
+    results, clocks, l0 = {}, None, native.launch_count
+    g = torch.Generator().manual_seed(11)
+    for name in (args.model.split(",") if args.model != "7b" else ["s", "m"]):
+        W, L, H, d, hkv, window, E, top, ff, V = KULANEX_SIZES[name]
+        max_ctx = -(-(prompt + 4 * (args.steps + args.warmup) * 4 + 64) // 128) * 128
+        ecfg = RaggedInferenceEngineConfig(state_manager={"max_ragged_batch_size": budget, "max_ragged_sequence_count": n_seqs, "max_tracked_sequences": n_seqs,
+                                                          "max_context": max_ctx, "memory_config": {"mode": "allocate", "size": n_seqs * (max_ctx // 128) + 4}})
+        res = {}
+        for fam in ("kulanex", "mixtral"):
+            cfg, sd = _kulanex_state(torch, dev, W, L, H, d, hkv, window, E, top, ff, V) if fam == "kulanex" else _mixtral_state(torch, dev, W, L, H, d, hkv, E, top, ff, V)
+            eng = build_engine_from_state_dict(fam, cfg, sd, ecfg, dtype=torch.bfloat16)
+            n_params = sum(v.numel() for v in sd.values())
+            del sd
+            prompts = [torch.randint(0, V, (prompt, ), generator=g).pin_memory() for _ in range(n_seqs)]
+            uids = list(range(n_seqs))
+            state = {"live": False, "next": None}
+
+            def prefill():
+                if state["live"]:
+                    for u in uids:
+                        eng.flush(u)
+                per = budget // prompt
+                nxt = torch.zeros(n_seqs, dtype=torch.long)
+                for i in range(0, n_seqs, per):
+                    us = uids[i:i + per]
+                    nxt[i:i + len(us)] = eng.put(us, [prompts[u] for u in us]).argmax(-1).cpu()
+                state["live"], state["next"] = True, nxt
+
+            def decode():
+                nxt = state["next"]
+                for _ in range(4):
+                    nxt = eng.put(uids, [nxt[u:u + 1] for u in uids]).argmax(-1).cpu()
+                state["next"] = nxt
+
+            ms_p, _ = _timed(torch, dist, prefill, args.steps, 3)
+            ms_d, clocks = _timed(torch, dist, decode, args.steps, args.warmup)
+            res[fam] = {"params_b": round(n_params / 1e9, 3), "prefill_tokens_per_s": round(n_seqs * prompt / ms_p * 1e3, 1), "prefill_ms": round(ms_p, 2),
+                        "decode_tokens_per_s": round(n_seqs * 4 / ms_d * 1e3, 1), "decode_ms_per_step": round(ms_d / 4, 3)}
+            del eng
+            torch.cuda.empty_cache()
+        res["kulanex_over_mixtral"] = {"prefill": round(res["kulanex"]["prefill_tokens_per_s"] / res["mixtral"]["prefill_tokens_per_s"], 3),
+                                       "decode": round(res["kulanex"]["decode_tokens_per_s"] / res["mixtral"]["decode_tokens_per_s"], 3)}
+        res["shape"] = {"width": W, "layers": L, "heads": H, "head_dim": d, "kv_heads": hkv, "window": window, "experts": E, "top": top, "ff": ff}
+        res["kernels"] = _kulanex_kernel_table(torch, peaks, W, H, d, hkv, window, E, top, ff, 4096, 2048, n_seqs)
+        results[name] = res
+    launches = native.launch_count - l0
+    last = results[list(results)[-1]]
+    extra = {"results": results, "peaks": {k: peaks[k] for k in ("hbm_gbs", "bf16_tflops", "source")},
+             "e2e": {"value": last["kulanex"]["decode_tokens_per_s"], "unit": "generated tokens/s", "h2d_bytes_per_step": n_seqs * 8, "d2h_bytes_per_step": n_seqs * 8},
+             "reference_arm": "none: the reference has no model of this design"}
+    config = {"model": "kulanex (random weights) beside mixtral of equal size", "sizes": list(results), "sequences": n_seqs, "prompt_len": prompt,
+              "token_budget_per_forward": budget, "decode_steps_per_timed_step": 4, "kv_block": 128,
+              "l2_policy": "engine steps: weights exceed the 126 MB L2, no flush; isolated kernels: 256 MB write before every timed run"}
+    print(json.dumps(_line("generated tokens/sec Kulanex FastGen ragged decode, 1 GPU (prefill and a Mixtral of equal size alongside)",
+                           last["kulanex"]["decode_tokens_per_s"], "tokens/s", 1, args, last["kulanex"]["decode_ms_per_step"], config, clocks, launches, extra)),
+          flush=True)
+
+
+WORKLOADS = {"fastgen70b": run_fastgen70b, "mixtral": run_mixtral, "ulysses13b": run_ulysses13b, "linasun": run_linasun, "kulanex": run_kulanex}

@@ -64,6 +64,9 @@ struct Params {
   int kv_planes;  // 2: a block holds a key plane and a value plane; 1: one plane serves as both (latent caches: keys == values)
   float scale_log2;
   int window;          // local attention: keys [pos - window + 1, pos] are visible; 0 = the whole history
+  int keep;            // with a window: the first `keep` keys of the sequence stay visible whatever their distance
+  long long out_ld;    // elements between the output rows of consecutive tokens (hq * D when the output is dense)
+  float out_scale;     // the normalised output is multiplied by this before it is rounded
   const float* alibi;  // optional [hq] ALiBi slopes: score += slope[head] * key position (BLOOM / MPT / falcon-rw); nullptr = none
   long long* trace;  // diagnostics only (DSB200_PF_TRACE=1): clock64 stamps of the first CTA with >= 8 pages, [page][8 events]
 };
@@ -158,9 +161,15 @@ paged_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int nt = *s_nt;
   // pages visible to the last token of the atom, and this CTA's slice of them
   const int n_pages = (pos0 + nt + BN - 1) / BN;
-  const int per_split = (n_pages + p.n_splits - 1) / p.n_splits;
+  // pages that can hold a visible key: with a window, the pages of the kept first keys and the pages from the window's start (of the
+  // atom's first token) on; list index j stands for page page_of(j)
+  const int win_pg = p.window > 0 ? max(0, pos0 + 1 - p.window) / BN : 0;
+  const int keep_pg = min((p.keep + BN - 1) / BN, win_pg);
+  const int n_list = keep_pg + (n_pages - win_pg);
+  auto page_of = [&](int j) { return j < keep_pg ? j : win_pg + (j - keep_pg); };
+  const int per_split = (n_list + p.n_splits - 1) / p.n_splits;
   const int pg0 = split * per_split;
-  const int pg1 = min(n_pages, pg0 + per_split);
+  const int pg1 = min(n_list, pg0 + per_split);
   const int n_blocks = max(0, pg1 - pg0);
   const bool partial = p.n_splits > 1;
   bool tracing = false;
@@ -191,7 +200,7 @@ paged_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             uint8_t* tile = smem + (is_v ? SMEM::V_OFF : SMEM::K_OFF) + st * SMEM::TILE;
             for (int s = 0; s < sub; ++s) {
               // blocks past the sequence's extent are never unmasked, but their bytes must be finite: re-read a valid block
-              const int logical = min((pg0 + j) * sub + s, last_blk);
+              const int logical = min(page_of(pg0 + j) * sub + s, last_blk);
               const int blk = bt[logical];
               const int row_off = s * p.block_size * 128;
 #pragma unroll
@@ -316,21 +325,23 @@ paged_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_wait(&s_full[b], (j >> 1) & 1);
         if (warp == 4 && lane == 0) { DSB_PF_TRACE(2, j) }
         tc_fence_after();
-        const int visible = limit - ((pg0 + j) * BN + part * 32);  // of this thread's 32 keys, [0, visible) count
+        const int key0 = page_of(pg0 + j) * BN + part * 32;  // first of this thread's 32 keys
+        const int visible = limit - key0;  // of this thread's 32 keys, [0, visible) count
         const uint32_t s_addr = TM_S + b * 128 + part * 32 + lane_off;
         uint32_t sv[32];  // the thread's scores stay in registers for both passes
         tmem_ld_32x32(s_addr, sv);
         tmem_ld_wait();
-        const int hidden = first - ((pg0 + j) * BN + part * 32);  // keys [0, hidden) of the thread's 32 precede the local window
+        const int hidden = first - key0;  // keys [0, hidden) of the thread's 32 precede the local window ...
+        const int kept = p.keep - key0;   // ... but its keys [0, kept) are kept first keys and stay visible
         if (!__all_sync(0xffffffffu, visible >= 32 && hidden <= 0)) {  // only the diagonal page(s) / the window's first page(s)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (i >= visible || i < hidden) sv[i] = 0xff800000u;  // -inf: exp2 gives exactly 0 below
+            if (i >= visible || (i < hidden && i >= kept)) sv[i] = 0xff800000u;  // -inf: exp2 gives exactly 0 below
         }
         if (has_alibi) {
-          const float key0 = static_cast<float>((pg0 + j) * BN + part * 32);
+          const float key0f = static_cast<float>(key0);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) sv[i] = __float_as_uint(fmaf(__uint_as_float(sv[i]), p.scale_log2, slope_l2 * (key0 + i)));
+          for (int i = 0; i < 32; ++i) sv[i] = __float_as_uint(fmaf(__uint_as_float(sv[i]), p.scale_log2, slope_l2 * (key0f + i)));
         }
         float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -406,8 +417,8 @@ paged_flash_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (live) {
         const int t = t0 + ti, head = kvh * p.group + g;
         if (!partial) {
-          const float inv_l = 1.f / l_run;
-          __nv_bfloat16* dst = p.out + (static_cast<size_t>(t) * p.hq + head) * D + part * DQ;
+          const float inv_l = p.out_scale / l_run;
+          __nv_bfloat16* dst = p.out + static_cast<size_t>(t) * p.out_ld + head * D + part * DQ;
 #pragma unroll
           for (int u = 0; u < DQ / 8; ++u) {
             uint4 val;
@@ -547,9 +558,15 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int nt = *s_nt;
   const int nq = nt * p.group;  // live columns
   const int n_pages = (pos0 + nt + BN - 1) / BN;
-  const int per_split = (n_pages + p.n_splits - 1) / p.n_splits;
+  // pages that can hold a visible key: with a window, the pages of the kept first keys and the pages from the window's start (of the
+  // atom's first token) on; list index j stands for page page_of(j)
+  const int win_pg = p.window > 0 ? max(0, pos0 + 1 - p.window) / BN : 0;
+  const int keep_pg = min((p.keep + BN - 1) / BN, win_pg);
+  const int n_list = keep_pg + (n_pages - win_pg);
+  auto page_of = [&](int j) { return j < keep_pg ? j : win_pg + (j - keep_pg); };
+  const int per_split = (n_list + p.n_splits - 1) / p.n_splits;
   const int pg0 = split * per_split;
-  const int pg1 = min(n_pages, pg0 + per_split);
+  const int pg1 = min(n_list, pg0 + per_split);
   const int n_blocks = max(0, pg1 - pg0);
   const bool partial = p.n_splits > 1;
   bool tracing = false;
@@ -579,7 +596,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             mbar_expect_tx(full, SMEM::TILE);
             uint8_t* tile = smem + (is_v ? SMEM::V_OFF : SMEM::K_OFF) + st * SMEM::TILE;
             for (int s = 0; s < sub; ++s) {
-              const int logical = min((pg0 + j) * sub + s, last_blk);
+              const int logical = min(page_of(pg0 + j) * sub + s, last_blk);
               const int blk = bt[logical];
               const int row_off = s * p.block_size * 128;
 #pragma unroll
@@ -682,13 +699,13 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         uint32_t sv[CPT];
         tmem_ld_32x4(s_addr0 + b * NQ, sv);
         tmem_ld_wait();
-        const int key = (pg0 + j) * BN + row;
+        const int key = page_of(pg0 + j) * BN + row;
         float s[CPT], wm[CPT];
         // column maxima over the 128 keys: one REDUX per column inside the warp (floats mapped monotonically to unsigned),
         // then the 4 lane-quarter warps meet in shared memory
 #pragma unroll
         for (int i = 0; i < CPT; ++i) {
-          s[i] = (key >= limit[i] || key < first[i]) ? -INFINITY : __uint_as_float(sv[i]);
+          s[i] = (key >= limit[i] || (key < first[i] && key >= p.keep)) ? -INFINITY : __uint_as_float(sv[i]);
           if (has_alibi) s[i] = fmaf(s[i], p.scale_log2, slope_l2[i] * static_cast<float>(key));
           const uint32_t bits = __float_as_uint(s[i]);
           const uint32_t r = __reduce_max_sync(0xffffffffu, bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u));
@@ -771,7 +788,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (c < nq) {
           const int t = t0 + c / p.group, head = kvh * p.group + c % p.group;
           if (!partial) {
-            p.out[(static_cast<size_t>(t) * p.hq + head) * D + row] = __float2bfloat16_rn(__uint_as_float(ov[i]) / l);
+            p.out[static_cast<size_t>(t) * p.out_ld + head * D + row] = __float2bfloat16_rn(__uint_as_float(ov[i]) / l * p.out_scale);
           } else {
             const size_t slot = (static_cast<size_t>(t) * p.hq + head) * p.n_splits + split;
             p.part_o[slot * D + row] = __uint_as_float(ov[i]);
@@ -803,7 +820,7 @@ paged_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 // out[t][h][:] = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s ; one warp per (token, head)
 template <int D>
 __global__ void combine_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
-                                      int rows, int n_splits) {
+                                      int rows, int n_splits, int hq, long long out_ld, float out_scale) {
   const int wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (wid >= rows) return;
   constexpr int EPL = D / 32;
@@ -822,16 +839,17 @@ __global__ void combine_splits_kernel(const float* __restrict__ part_o, const fl
 #pragma unroll
     for (int e = 0; e < EPL; ++e) acc[e] = fmaf(w, part_o[slot * D + lane * EPL + e], acc[e]);
   }
-  const float inv = 1.f / L;
+  const float inv = out_scale / L;
+  __nv_bfloat16* dst = out + static_cast<size_t>(wid / hq) * out_ld + (wid % hq) * D;
 #pragma unroll
-  for (int e = 0; e < EPL; ++e) out[static_cast<size_t>(wid) * D + lane * EPL + e] = __float2bfloat16_rn(acc[e] * inv);
+  for (int e = 0; e < EPL; ++e) dst[lane * EPL + e] = __float2bfloat16_rn(acc[e] * inv);
 }
 
 template <int D>
 static int launch(const void* qkv, const void* kv_cache, void* out, const int* tok_seq, const int* tok_pos, const int* block_table,
                   int T, int hq, int hkv, int block_size, int max_blocks, int num_blocks, float scale, int max_atoms, int n_splits,
                   void* scratch, const float* alibi, int window, cudaStream_t stream, int q_heads = 0, long long q_head_stride = 0,
-                  long long q_tok_stride = 0, int kv_planes = 2) {
+                  long long q_tok_stride = 0, int kv_planes = 2, int keep = 0, long long out_ld = 0, float out_scale = 1.f) {
   using SMEM = Smem<D>;
   const int group = hq / hkv, nt_tile = BM / group;
   // the query tensor: [T][heads][D] rows of the fused projection by default; callers may give the number of heads that exist (a box
@@ -874,6 +892,7 @@ static int launch(const void* qkv, const void* kv_cache, void* out, const int* t
   p.out = static_cast<__nv_bfloat16*>(out); p.part_o = part_o; p.part_ml = part_ml;
   p.T = T; p.hq = hq; p.hkv = hkv; p.group = group; p.nt_tile = nt_tile; p.block_size = block_size; p.max_blocks = max_blocks;
   p.n_splits = n_splits; p.kv_planes = kv_planes; p.scale_log2 = scale * 1.4426950408889634f; p.alibi = alibi; p.window = window;
+  p.keep = window > 0 ? keep : 0; p.out_ld = out_ld ? out_ld : static_cast<long long>(hq) * D; p.out_scale = out_scale;
   static const bool want_trace = [] { const char* e = getenv("DSB200_PF_TRACE"); return e && atoi(e) != 0; }();
   static long long* trace_buf = nullptr;
   p.trace = nullptr;
@@ -897,7 +916,8 @@ static int launch(const void* qkv, const void* kv_cache, void* out, const int* t
   }
   if (n_splits > 1) {
     const int rows = T * hq;
-    combine_splits_kernel<D><<<(rows * 32 + 255) / 256, 256, 0, stream>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), rows, n_splits);
+    combine_splits_kernel<D><<<(rows * 32 + 255) / 256, 256, 0, stream>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), rows, n_splits, hq, p.out_ld,
+                                                                          p.out_scale);
     DSB_CHECK_CUDA(cudaGetLastError());
   }
   return DSB_OK;
@@ -907,7 +927,8 @@ static int launch(const void* qkv, const void* kv_cache, void* out, const int* t
 static int launch_decode(const void* qkv, const void* kv_cache, void* out, const int* tok_seq, const int* tok_pos, const int* block_table,
                          int T, int hq, int hkv, int block_size, int max_blocks, int num_blocks, float scale, int max_atoms,
                          int n_splits, void* scratch, const float* alibi, int window, cudaStream_t stream, int q_heads = 0,
-                         long long q_head_stride = 0, long long q_tok_stride = 0, int kv_planes = 2) {
+                         long long q_head_stride = 0, long long q_tok_stride = 0, int kv_planes = 2, int keep = 0, long long out_ld = 0,
+                         float out_scale = 1.f) {
   constexpr int D = 128;
   const int group = hq / hkv, nt_tile = NQ / group;
   const int heads = q_heads ? q_heads : hq + 2 * hkv;
@@ -943,6 +964,7 @@ static int launch_decode(const void* qkv, const void* kv_cache, void* out, const
   p.out = static_cast<__nv_bfloat16*>(out); p.part_o = part_o; p.part_ml = part_ml;
   p.T = T; p.hq = hq; p.hkv = hkv; p.group = group; p.nt_tile = nt_tile; p.block_size = block_size; p.max_blocks = max_blocks;
   p.n_splits = n_splits; p.kv_planes = kv_planes; p.scale_log2 = scale * 1.4426950408889634f; p.trace = nullptr; p.alibi = alibi; p.window = window;
+  p.keep = window > 0 ? keep : 0; p.out_ld = out_ld ? out_ld : static_cast<long long>(hq) * D; p.out_scale = out_scale;
   static const bool want_trace = [] { const char* e = getenv("DSB200_PF_TRACE"); return e && atoi(e) != 0; }();
   static long long* trace_buf = nullptr;
   if (want_trace) {
@@ -965,7 +987,8 @@ static int launch_decode(const void* qkv, const void* kv_cache, void* out, const
   }
   if (n_splits > 1) {
     const int rows = T * hq;
-    combine_splits_kernel<D><<<(rows * 32 + 255) / 256, 256, 0, stream>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), rows, n_splits);
+    combine_splits_kernel<D><<<(rows * 32 + 255) / 256, 256, 0, stream>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), rows, n_splits, hq, p.out_ld,
+                                                                          p.out_scale);
     DSB_CHECK_CUDA(cudaGetLastError());
   }
   return DSB_OK;
@@ -1048,4 +1071,33 @@ DSB_EXPORT int dsb200_paged_flash_latent(const void* q, int q_heads, long long q
                               scale, max_atoms, n_splits, scratch, nullptr, 0, stream, q_heads, q_head_stride, q_tok_stride, 1);
   return paged::launch<64>(q, cache, out, tok_seq, tok_pos, block_table, n_tokens, heads, 1, block_size, max_blocks_per_seq, num_blocks, scale,
                            max_atoms, n_splits, scratch, nullptr, 0, stream, q_heads, q_head_stride, q_tok_stride, 1);
+}
+
+// Sliding-window attention that keeps the first keys visible, on the tensor-core kernels: a query at position p sees the keys j <= p with
+// p - j < window or j < keep_first.  q [n_tokens][hq][head_dim] bf16 at q_tok_stride elements per token (a multiple of 8), kv_cache
+// [num_blocks][2][block_size][hkv][head_dim] bf16; out rows at out_ld elements per token (a multiple of 8), multiplied by out_scale before
+// rounding.  Only the pages of the kept keys and of the window are visited.  decode != 0 selects the small-atom kernel (head_dim 128, q:kv
+// head ratio dividing 16).  Scratch and atoms as for dsb200_paged_flash_attention.
+DSB_EXPORT int dsb200_paged_flash_window(const void* q, long long q_tok_stride, const void* kv_cache, void* out, long long out_ld, const int* tok_seq,
+                                         const int* tok_pos, const int* block_table, int n_tokens, int hq, int hkv, int head_dim, int block_size,
+                                         int max_blocks_per_seq, int num_blocks, float scale, float out_scale, int window, int keep_first,
+                                         int max_atoms, int n_splits, void* scratch, int decode, cudaStream_t stream) {
+  using namespace dsb;
+  if (n_tokens == 0) return DSB_OK;
+  DSB_REQUIRE(head_dim == 64 || head_dim == 128, "paged_flash_window: head_dim %d unsupported (64 or 128)", head_dim);
+  DSB_REQUIRE(hq % hkv == 0 && 128 % (hq / hkv) == 0, "paged_flash_window: q/kv head ratio %d must divide 128", hq / hkv);
+  DSB_REQUIRE(block_size >= 8 && block_size <= 128 && 128 % block_size == 0, "paged_flash_window: KV block size %d must divide 128", block_size);
+  DSB_REQUIRE(window >= 1 && keep_first >= 0 && q_tok_stride % 8 == 0 && out_ld % 8 == 0 && out_ld >= static_cast<long long>(hq) * head_dim,
+              "paged_flash_window: window %d, kept %d, strides %lld / %lld", window, keep_first, q_tok_stride, out_ld);
+  DSB_REQUIRE(max_atoms >= 1 && n_splits >= 1 && n_splits <= 64 && scratch != nullptr, "paged_flash_window: bad max_atoms / n_splits / scratch");
+  if (decode) {
+    DSB_REQUIRE(head_dim == 128 && 16 % (hq / hkv) == 0, "paged_flash_window: the decode kernel takes head_dim 128 and head ratios dividing 16");
+    return paged::launch_decode(q, kv_cache, out, tok_seq, tok_pos, block_table, n_tokens, hq, hkv, block_size, max_blocks_per_seq, num_blocks, scale,
+                                max_atoms, n_splits, scratch, nullptr, window, stream, hq, head_dim, q_tok_stride, 2, keep_first, out_ld, out_scale);
+  }
+  if (head_dim == 128)
+    return paged::launch<128>(q, kv_cache, out, tok_seq, tok_pos, block_table, n_tokens, hq, hkv, block_size, max_blocks_per_seq, num_blocks, scale,
+                              max_atoms, n_splits, scratch, nullptr, window, stream, hq, head_dim, q_tok_stride, 2, keep_first, out_ld, out_scale);
+  return paged::launch<64>(q, kv_cache, out, tok_seq, tok_pos, block_table, n_tokens, hq, hkv, block_size, max_blocks_per_seq, num_blocks, scale,
+                           max_atoms, n_splits, scratch, nullptr, window, stream, hq, head_dim, q_tok_stride, 2, keep_first, out_ld, out_scale);
 }

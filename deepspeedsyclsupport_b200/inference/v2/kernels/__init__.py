@@ -452,6 +452,7 @@ def moe_gemm_rows(x, w, cumsum):
 # [n_seqs, 4] int32 (first row, new tokens, tokens seen before, state slot).
 native.register_sigs({
     "dsb200_scan_state_floats": "ii",
+    "dsb200_paged_flash_window": "p l pp l ppp iiiiiii ff ii ii p i p",
     "dsb200_window_qk_prepare": "p l ii pppp p ppp p ii pp l p iiiiii f i p",
     "dsb200_conv_state_update": "p l i p ii p iii i p",
     "dsb200_window_attention": "p l p ppp ii p l iiiiii ff i p",
@@ -503,6 +504,36 @@ def window_attention(q, cache, tok_seq, tok_pos, block_table, out, H, G, d, wind
                                                       native.ptr(block_table), block_table.stride(0), cache.shape[2], native.ptr(out),
                                                       out.stride(0), T, H, G, d, int(window), int(keep_first), float(scale), float(out_scale),
                                                       _dt(q), native.stream_ptr()))
+    return out
+
+
+def paged_flash_window_ok(q, cache, out, H, G, d):
+    """Whether the tensor-core kernels take this windowed attention: bf16, head size 64 / 128, a q:kv head ratio dividing 128, cache blocks
+    dividing 128, 16-byte aligned rows."""
+    return (q.is_cuda and q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and d in (64, 128) and H % G == 0 and
+            128 % (H // G) == 0 and cache.shape[2] >= 8 and 128 % cache.shape[2] == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and
+            q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0 and os.environ.get("DSB200_PAGED_FLASH", "1") != "0")
+
+
+def paged_flash_window(q, cache, tok_seq, tok_pos, block_table, out, H, G, d, window, keep_first, scale, out_scale=1.0, decode=False, max_context=None,
+                       n_splits=None):
+    """`window_attention` on the tensor cores (csrc/attn/paged_flash.cu: TMA pages through the block table, S / P / O in TMEM); only the
+    pages of the kept first keys and of the window are visited.  `decode`: (almost) one token per sequence -- the small-atom kernel."""
+    T = q.shape[0]
+    bs, group = cache.shape[2], H // G
+    decode = bool(decode) and d == 128 and 16 % group == 0 and os.environ.get("DSB200_PAGED_DECODE", "1") != "0"
+    nt = (16 if decode else 128) // group
+    max_atoms = max(1, min(T, (T + nt - 1) // nt + block_table.shape[0]))
+    if n_splits is None:
+        ctx = max_context if max_context is not None else block_table.shape[1] * bs
+        pages = -(-min(ctx, window + keep_first + 256) // 128)
+        n_splits = _pick_splits(T, H, d, max_atoms * G, pages, page_us=0.45 if decode else 0.7)
+    nbytes = native.lib().dsb200_paged_flash_scratch_bytes(T, H, d, max_atoms, n_splits)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    native.check(native.lib().dsb200_paged_flash_window(native.ptr(q), q.stride(0), native.ptr(cache), native.ptr(out), out.stride(0), native.ptr(tok_seq),
+                                                        native.ptr(tok_pos), native.ptr(block_table), T, H, G, d, bs, block_table.shape[1], cache.shape[0],
+                                                        float(scale), float(out_scale), int(window), int(keep_first), max_atoms, n_splits,
+                                                        native.ptr(scratch), int(decode), native.stream_ptr()), 2 + (n_splits > 1))
     return out
 
 

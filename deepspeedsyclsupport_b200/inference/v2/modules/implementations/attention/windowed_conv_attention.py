@@ -4,7 +4,11 @@ a whole-projection RMS norm and an interleaved partial rotation, and whose value
 Per layer and step: `window_qk_prepare` (convolution from the batch rows and the sequence's kept rows; values into cache plane 1; norms;
 rotation with angles formed in double precision; keys into plane 0), `conv_state_update`, then the attention kernel over the visible keys
 [0, keep_first) + the last `window`.  The cache is [blocks, 2, block_size, kv_heads, head_size], the layout of the dense attention's
-cache, so both kinds of layer share the block ids of a sequence.  csrc/ragged/recurrent_ops.cu."""
+cache, so both kinds of layer share the block ids of a sequence.  csrc/ragged/recurrent_ops.cu.
+
+Two attention kernels.  bf16 with head size 64 / 128: the tcgen05 paged flash kernels (csrc/attn/paged_flash.cu) with the window, the kept
+keys and a page list that skips what lies between them.  Everything else (fp32, other head sizes): `window_attention`, a CUDA-core kernel
+with fp32 scores and accumulation that takes any size."""
 import math
 from typing import Any, Dict, List, Type
 
@@ -32,6 +36,13 @@ def scaled_rotary_frequencies(rotate_dim, theta_base, scaling=None):
                 f = (1.0 - s) * f / scaling.factor + s * f
         out.append(f)
     return torch.tensor(out, dtype=torch.float64)
+
+
+def windowed_attention(q, kv_cache, tok_seq, tok_pos, block_table, out, H, G, d, window, keep_first, scale, out_scale=1.0, decode=False):
+    """Attention of q [T, H d] over the paged cache with the sliding window and the kept first keys, into `out` (a [T, H d] view)."""
+    if K.paged_flash_window_ok(q, kv_cache, out, H, G, d):
+        return K.paged_flash_window(q, kv_cache, tok_seq, tok_pos, block_table, out, H, G, d, window, keep_first, scale, out_scale=out_scale, decode=decode)
+    return K.window_attention(q, kv_cache, tok_seq, tok_pos, block_table, out, H, G, d, window, keep_first, scale, out_scale=out_scale)
 
 
 @DSSelfAttentionRegistry.register_module
@@ -94,5 +105,5 @@ class DSWindowedConvAttention(DSSelfAttentionBase):
                             kv_cache, q, self._freq, H, G, d, c.conv_taps, c.rotate_dim, c.eps)
         if conv_state is not None:
             K.conv_state_update(proj, q0, self.conv_channels, conv_state, 0, desc, batch.current_sequences, c.conv_taps)
-        return K.window_attention(q, kv_cache, batch.tok_seq(), batch.tok_pos(), batch.block_table(), out, H, G, d, c.window, c.keep_first,
-                                  c.scale, out_scale=c.out_scale)
+        return windowed_attention(q, kv_cache, batch.tok_seq(), batch.tok_pos(), batch.block_table(), out, H, G, d, c.window, c.keep_first, c.scale,
+                                  out_scale=c.out_scale, decode=batch.current_tokens <= 2 * batch.current_sequences)

@@ -155,6 +155,16 @@ int dsb200_paged_flash_latent(const void* q, int q_heads, long long q_head_strid
                               const void* cache, void* out, const int* tok_seq, const int* tok_pos, const int* block_table,
                               int n_tokens, int heads, int rank, int block_size, int max_blocks_per_seq, int num_blocks,
                               float scale, int max_atoms, int n_splits, void* scratch, int decode, dsb200_stream_t stream);
+/* Sliding-window attention that keeps the first keys visible, on the tensor-core kernels: a query at position p sees the keys j <= p with
+ * p - j < window or j < keep_first.  q [n_tokens][hq][head_dim] bf16 at q_tok_stride elements per token (a multiple of 8), kv_cache
+ * [num_blocks][2][block_size][hkv][head_dim] bf16; out rows at out_ld elements per token (a multiple of 8), multiplied by out_scale before
+ * rounding.  Only the pages of the kept keys and of the window are visited.  decode != 0 selects the small-atom kernel (head_dim 128, q:kv
+ * head ratio dividing 16).  Scratch and atoms as for dsb200_paged_flash_attention. */
+int dsb200_paged_flash_window(const void* q, long long q_tok_stride, const void* kv_cache, void* out, long long out_ld,
+                              const int* tok_seq, const int* tok_pos, const int* block_table, int n_tokens, int hq,
+                              int hkv, int head_dim, int block_size, int max_blocks_per_seq, int num_blocks, float scale,
+                              float out_scale, int window, int keep_first, int max_atoms, int n_splits, void* scratch,
+                              int decode, dsb200_stream_t stream);
 
 /* ---- csrc/comm/symm.cu */
 /* ---- allocation / mapping (host pointers unless noted) */

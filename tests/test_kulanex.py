@@ -288,6 +288,9 @@ ATTN = {
     "plain": O.parallel_layer(heads=1, kv_heads=1, dim=8, conv=1, window=500, keep_first=0, rot_dims=8, scale=0.35)["mixer"]["left"],
     # no rotation at all, more kept tokens than the window is long, two taps
     "sinks": O.parallel_layer(heads=4, kv_heads=4, dim=16, conv=2, window=5, keep_first=9, rot_dims=0, scale=0.25)["mixer"]["left"],
+    # head sizes the tensor-core kernels take in bf16: grouped heads, a window that ends inside a 128-key page, kept keys
+    "tc64": O.parallel_layer(heads=4, kv_heads=2, dim=64, conv=3, window=21, keep_first=2, rot_dims=32, scale=0.125)["mixer"]["left"],
+    "tc128": O.parallel_layer(heads=8, kv_heads=1, dim=128, conv=4, window=50, keep_first=5, rot_dims=64, base=1e5, scale=0.09)["mixer"]["left"],
 }
 
 
@@ -317,41 +320,69 @@ def test_output_constant_of_the_attention():
 
 
 @gpu
-@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("d,dt", [(8, torch.float32), (8, torch.bfloat16), (64, torch.bfloat16), (128, torch.bfloat16)])
 @pytest.mark.parametrize("decode", [False, True])
-@pytest.mark.parametrize("window,keep", [(40, 4), (64, 1), (17, 0), (300, 2)])
-def test_window_and_kept_edges_decide_what_is_seen(window, keep, decode, dt):
+@pytest.mark.parametrize("window,keep", [(40, 4), (64, 1), (17, 0), (300, 2), (130, 3)])
+def test_window_and_kept_edges_decide_what_is_seen(window, keep, decode, d, dt):
     """One key is made to dominate its row's softmax (its direction is planted in key and query, its value is a marker): the output shows
     the marker exactly when the key is visible -- the last key inside the window, the first outside, the last kept token, the first not
-    kept, keys at both sides of a page border and a far one; in a prompt portion and for a single decoded token."""
+    kept, keys at both sides of block and 128-key page borders and a far one; in a prompt portion and for a single decoded token; on the
+    CUDA-core kernel (head size 8) and on the tensor-core kernels (64, 128: the decode kernel too)."""
+    from deepspeedsyclsupport_b200.inference.v2.modules.implementations.attention.windowed_conv_attention import windowed_attention
     K = _K()
-    H, G, d, block, T = 2, 1, 8, 16, 150
-    blocks = [3, 7, 1, 12, 5, 9, 0, 4, 8, 2]
+    H, G, block, T = 2, 1, 16, 300
+    blocks = [3, 7, 1, 12, 5, 9, 0, 4, 8, 2, 19, 14, 11, 17, 6, 10, 13, 15, 16]
     g = torch.Generator().manual_seed(window)
     kk = torch.randn(T, d, generator=g) * 0.1
     vv = torch.randn(T, d, generator=g) * 0.1
     query_pos = T - 1
-    targets = {query_pos - window + 1, query_pos - window, keep - 1, keep, 15, 16, 31, 32, 60, query_pos}
+    targets = {query_pos - window + 1, query_pos - window, keep - 1, keep, 15, 16, 127, 128, 255, 256, 60, query_pos}
     for target in sorted(t for t in targets if 0 <= t < T):
         k2, v2 = kk.clone(), vv.clone()
         k2[target] = torch.tensor([6.0] + [0.0] * (d - 1))
         v2[target] = 50.0
-        cache = torch.zeros(16, 2, block, G, d, dtype=dt, device="cuda")
-        for p in range(T):
-            cache[blocks[p // block], 0, p % block, 0] = k2[p].to(dt).cuda()
-            cache[blocks[p // block], 1, p % block, 0] = v2[p].to(dt).cuda()
+        cache = torch.zeros(20, 2, block, G, d, dtype=dt, device="cuda")
+        pages = torch.tensor(blocks)[torch.arange(T) // block]
+        cache[pages, 0, torch.arange(T) % block, 0] = k2.to(dt).cuda()
+        cache[pages, 1, torch.arange(T) % block, 0] = v2.to(dt).cuda()
         n_new = 1 if decode else 23
         q = torch.zeros(n_new, H * d)
         q[:, 0] = q[:, d] = 6.0
         out = torch.empty(n_new, H * d, dtype=dt, device="cuda")
-        K.window_attention(q.to(dt).cuda(), cache, *[getattr(_Batch([(0, T - n_new, n_new, blocks)], block, 10), f)() for f in ("tok_seq", "tok_pos", "block_table")],
-                           out, H, G, d, window, keep, 1.0)
+        b = _Batch([(0, T - n_new, n_new, blocks)], block, len(blocks))
+        qd = q.to(dt).cuda()
+        if d == 8:
+            K.window_attention(qd, cache, b.tok_seq(), b.tok_pos(), b.block_table(), out, H, G, d, window, keep, 1.0)
+        else:
+            assert K.paged_flash_window_ok(qd, cache, out, H, G, d)
+            windowed_attention(qd, cache, b.tok_seq(), b.tok_pos(), b.block_table(), out, H, G, d, window, keep, 1.0, decode=decode)
         visible = target <= query_pos and (query_pos - target < window or target < keep)
         row = out[-1].float().cpu()
         assert bool((row > 40).all()) == visible and bool((row.abs() < 1).all()) == (not visible), (target, visible, row)
         ks, vs = k2.to(dt).double(), v2.to(dt).double()
         s = (ks[:T] @ q[-1, :d].to(dt).double()).masked_fill(~O.window_visible(T, window, keep)[query_pos], float("-inf"))
         assert torch.allclose(row[:d].double(), torch.softmax(s, -1) @ vs, rtol=2e-2 if dt == torch.bfloat16 else 1e-4, atol=2e-2 if dt == torch.bfloat16 else 1e-5)
+
+
+@gpu
+@pytest.mark.parametrize("d,G", [(64, 2), (128, 1)])
+def test_tensor_core_and_cuda_core_attention_agree_on_a_mixed_batch(d, G):
+    """Portions of unequal sequences beside single tokens, strided output with a constant: both kernels give the same rows."""
+    from deepspeedsyclsupport_b200.inference.v2.modules.implementations.attention.windowed_conv_attention import windowed_attention
+    K = _K()
+    H, block, window, keep = 4, 32, 70, 3
+    seqs = [(0, 150, 40, [5, 1, 9, 3, 7, 11]), (1, 0, 9, [0]), (2, 99, 1, [2, 4, 6, 8]), (3, 255, 1, [10, 12, 13, 14, 15, 16, 17, 18])]
+    b = _Batch(seqs, block, 8)
+    g = torch.Generator().manual_seed(d)
+    cache = (torch.randn(20, 2, block, G, d, generator=g) * 0.5).bfloat16().cuda()
+    q = torch.randn(b.current_tokens, H * d, generator=g).bfloat16().cuda()
+    wide = torch.zeros(b.current_tokens, H * d + 24, dtype=torch.bfloat16, device="cuda")
+    ref = torch.empty(b.current_tokens, H * d, dtype=torch.bfloat16, device="cuda")
+    K.window_attention(q, cache, b.tok_seq(), b.tok_pos(), b.block_table(), ref, H, G, d, window, keep, d ** -0.5, out_scale=1.3)
+    for decode in (False, True):
+        wide.zero_()
+        windowed_attention(q, cache, b.tok_seq(), b.tok_pos(), b.block_table(), wide[:, :H * d], H, G, d, window, keep, d ** -0.5, out_scale=1.3, decode=decode)
+        assert _rel(wide[:, :H * d], ref.cpu().double()) < 1.5e-2 and float(wide[:, H * d:].abs().max()) == 0
 
 
 def _memory_module(m, dt, out_scale=1.0):
@@ -488,6 +519,7 @@ CONFIGS = {
         O.delta_layer(heads=4, kv_heads=4, dim=32, vdim=32, conv=4, mlp=O.moe(8, 2, 32)),
         O.parallel_layer(heads=4, kv_heads=2, dim=64, conv=4, window=33, keep_first=2, rot_dims=32, base=1e5, scaling={"factor": 5.0, "low": 1.0, "high": 3.0, "original": 128},
                          scale=0.11, r_heads=2, r_dim=32, r_vdim=48, mlp=O.moe(8, 2, 32)),
+        O.parallel_layer(heads=2, kv_heads=1, dim=128, conv=2, window=140, keep_first=3, rot_dims=128, scale=0.09, r_heads=1, r_dim=16, r_vdim=32),
     ], vocab=96, width=128, eps=1e-6, residual_mult=1.0),
     # no attention layer at all: nothing is cached per token, everything lives in the state slots
     "recurrent": O.make_config([O.delta_layer(heads=2, kv_heads=1, dim=8, vdim=8, conv=2), O.delta_layer(heads=2, kv_heads=2, dim=4, vdim=12, conv=3, mlp=O.moe(2, 1, 8))],
