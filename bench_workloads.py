@@ -650,18 +650,20 @@ def _kulanex_kernel_table(torch, peaks, W, H, d, hkv, window, E, top, ff, T, ctx
         bp, ap = torch.randn(Tn, H, device=dev), torch.randn(Tn, H * d, device=dev)
         Al, dtb = torch.full((H, ), -2.5, device=dev), torch.full((H * d, ), -2.0, device=dev)
         dS = torch.zeros(n_seq, H, K.scan_state_floats(d, d), device=dev)
-        add(f"delta_rule_scan ({H} x {d} x {d}), {label}", _event_ms(torch, lambda: K.delta_rule_scan(qn, kn, vv, bp, ap, Al, dtb, desc, n_seq, dS, H, H, d, d), 5, flush),
+        bp, ap = torch.sigmoid(bp), torch.exp(-0.08 * torch.nn.functional.softplus(ap - 2.0))  # betas and decays as delta_prepare leaves them
+        add(f"delta_rule_scan ({H} x {d} x {d}), {label}", _event_ms(torch, lambda: K.delta_rule_scan(qn, kn, vv, bp, ap, desc, n_seq, dS, H, H, d, d), 5, flush),
             f"paged flash attention, {label}", like_ms, nbytes=Tn * H * (4 * d * 4 + 4) + Tn * H * d * 4 + n_seq * H * d * d * 8, like_bytes=like_frac_b,
             flops=0, like_flops=4.0 * keys * H * d)
         p3 = torch.randn(Tn, 3 * H * d, device=dev).to(bf)
         c3 = torch.randn(3 * H * d, 4, device=dev)
         st3 = torch.zeros(n_seq, 3, 3 * H * d, device=dev, dtype=bf)
+        ap2, bp2 = torch.randn(Tn, H * d, device=dev), torch.randn(Tn, H, device=dev)
 
         def dprep():
-            K.delta_prepare(p3, 0, H * d, 2 * H * d, c3, c3[H * d:], c3[2 * H * d:], st3, desc, tok_seq, H, H, d, d, 4)
+            K.delta_prepare(p3, 0, H * d, 2 * H * d, c3, c3[H * d:], c3[2 * H * d:], st3, desc, tok_seq, ap2, bp2, Al, dtb, H, H, d, d, 4)
             K.conv_state_update(p3, 0, 3 * H * d, st3, 0, desc, n_seq, 4)
         add(f"delta_prepare + conv_state_update, {label}", _event_ms(torch, dprep, 10, flush), f"kv_rotary_append, {label}", rows[-4]["like_ms"],
-            nbytes=Tn * 3 * H * d * (2 + 4), like_bytes=Tn * (H + 2 * hkv) * d * 4)
+            nbytes=Tn * (3 * H * d * (2 + 4) + H * d * 8), like_bytes=Tn * (H + 2 * hkv) * d * 4)
         o32, gt, og = torch.randn(Tn, H * d, device=dev), torch.randn(Tn, H * d, device=dev).to(bf), torch.empty(Tn, H * d, device=dev, dtype=bf)
         add(f"head_norm_gate, {label}", _event_ms(torch, lambda: K.head_norm_gate(o32, nw[:d].contiguous(), gt, og, H, d, 1e-6, shared_weight=True), 10, flush),
             "gated_act (silu)", _event_ms(torch, lambda: FO.gated_act(torch.cat([gt, gt], 1) if False else qkv[:, :2 * (H * d // 2)].contiguous(), "silu"), 10, flush),

@@ -94,12 +94,14 @@ template <typename T>
 __device__ __forceinline__ float conv_at(const T* __restrict__ u, long long ld, const T* __restrict__ st, int st_ld,
                                          const float* __restrict__ w, int taps, int i, int seen) {
   float acc = 0.f;
+#pragma unroll 4
   for (int j = 0; j < taps; ++j) {
     const int ii = i - (taps - 1) + j;
-    float v = 0.f;
-    if (ii >= 0) v = to_f(u[static_cast<long long>(ii) * ld]);
-    else if (seen + ii >= 0) v = to_f(st[(taps - 1 + ii) * st_ld]);
-    acc = fmaf(w[j], v, acc);
+    // one load per tap from a pointer chosen without a branch (the current row stands in where nothing exists), so the loads of all taps
+    // are in flight together
+    const T* src = ii >= 0 ? u + static_cast<long long>(ii) * ld : (seen + ii >= 0 ? st + (taps - 1 + ii) * st_ld : u + static_cast<long long>(i) * ld);
+    const float v = to_f(*src);
+    acc = fmaf(w[j], (ii >= 0 || seen + ii >= 0) ? v : 0.f, acc);
   }
   return acc;
 }
@@ -159,10 +161,14 @@ __global__ void window_qk_prepare_kernel(const T* __restrict__ proj, long long l
     }
   }
   for (int f = threadIdx.x; f < rot_dims / 2; f += blockDim.x) {
-    double s, c;
-    sincos(static_cast<double>(pos) * freq[f], &s, &c);
-    cs[f] = static_cast<float>(c);
-    sn[f] = static_cast<float>(s);
+    // the angle is formed and brought into [-pi, pi] in double (a position in the thousands times a frequency near one loses the low
+    // bits of a float); sine and cosine of the reduced angle are then taken in single precision
+    const double ang = static_cast<double>(pos) * freq[f];
+    const float red_ang = static_cast<float>(ang - 6.283185307179586476925 * rint(ang * 0.15915494309189533577));
+    float s, c;
+    sincosf(red_ang, &s, &c);
+    cs[f] = c;
+    sn[f] = s;
   }
   sq = block_sum(sq, red);
   sk = block_sum(sk, red);  // (the barriers inside also publish y, cs, sn)
@@ -254,11 +260,12 @@ window_attention_kernel(const T* __restrict__ q, long long q_ld, const T* __rest
 
 // --------------------------------------------------------------------------------------------------------- recurrent scans
 // A block owns SCAN_THREADS / R columns of the d x dv state of one (sequence, head) and walks the sequence's new tokens in order (the
-// columns of these recurrences do not interact).  Thread (col, r) -- r varying fastest, R a power of two <= 32 -- holds rows r, r + R, ...
-// of its column in registers; sums over rows are finished by a butterfly over the R lanes.  The state is kept in global memory in thread
-// order ([column tile][RPT][SCAN_THREADS], opaque to everything but these kernels, coalesced); inputs of SCAN_CHUNK tokens at a time are
-// staged in shared memory.
-constexpr int SCAN_CHUNK = 8, SCAN_THREADS = 256;
+// columns of these recurrences do not interact).  Thread (col, r) -- r varying fastest, R a power of two <= 32 -- holds rows r RPT ..
+// r RPT + RPT - 1 of its column in registers (its q / k values are consecutive in shared memory: 16-byte loads); sums over rows are finished by a butterfly over the R lanes.  The state is kept in global memory in thread
+// order ([column tile][RPT][SCAN_THREADS], opaque to everything but these kernels, coalesced).  Inputs travel in chunks of `ch` tokens
+// (a power of two <= 16 with at most SCAN_PF * SCAN_THREADS staged values per array): while a chunk is consumed from shared memory the
+// next one is already on its way in registers, so the walk never waits for global memory.
+constexpr int SCAN_THREADS = 256, SCAN_PF = 8;
 
 template <int R>
 __device__ __forceinline__ float lanes_sum(float v) {
@@ -268,148 +275,281 @@ __device__ __forceinline__ float lanes_sum(float v) {
 }
 
 // q / k at columns q_col0 / k_col0 of proj (H x d each), v at v_col0 (H x dv); gates: pre-activations [T, 2 H] fp32 (input gate | forget
-// gate) without their biases.  state_S [slots, H, RPT * threads], state_n [slots, H, d], state_m [slots, H].  out fp32 [T, H dv].
+// gate) without their biases.  state_S [slots, H, tiles * RPT * SCAN_THREADS], state_n [slots, H, d], state_m [slots, H].  out fp32
+// [T, H dv].  The block has one warp more than SCAN_THREADS: it walks the gate recurrence (m, the two decay factors and exp(-m) of every
+// token, three exponentials each) of the NEXT chunk while the others consume the current one.
 template <typename T, int RPT, int R>
-__global__ void __launch_bounds__(SCAN_THREADS)
-matrix_memory_scan_kernel(const T* __restrict__ proj, long long ld, int q_col0, int k_col0, int v_col0,
-                                          const float* __restrict__ gates, const float* __restrict__ bias_i, const float* __restrict__ bias_f,
-                                          float cap, const int4* __restrict__ seq_desc, float* __restrict__ state_S, float* __restrict__ state_n,
-                                          float* __restrict__ state_m, float* __restrict__ out, int H, int d, int dv) {
-  extern __shared__ float sm[];
+__global__ void __launch_bounds__(SCAN_THREADS + 32, RPT <= 16 ? 2 : 1)
+matrix_memory_scan_kernel(const T* __restrict__ proj, long long ld, int q_col0, int k_col0, int v_col0, const float* __restrict__ gates,
+                          const float* __restrict__ bias_i, const float* __restrict__ bias_f, float cap, const int4* __restrict__ seq_desc,
+                          float* __restrict__ state_S, float* __restrict__ state_n, float* __restrict__ state_m, float* __restrict__ out, int H, int d,
+                          int dv, int ch) {
+  extern __shared__ __align__(16) float sm[];
+  constexpr int nthr = SCAN_THREADS, CB = nthr / R, DP = R * RPT;  // DP: a staged q / k row, padded with zeros past d
   const int4 sd = seq_desc[blockIdx.x];
   const int h = blockIdx.y, tid = threadIdx.x;
-  constexpr int nthr = SCAN_THREADS;
-  const int col = blockIdx.z * (nthr / R) + tid / R, r = tid % R;
-  const bool live = col < dv;
-  float* qs = sm;                        // [CHUNK][d]
-  float* ks = qs + SCAN_CHUNK * d;       // [CHUNK][d]
-  float* vs = ks + SCAN_CHUNK * d;       // [CHUNK][dv]
-  float* gi = vs + SCAN_CHUNK * dv;      // [CHUNK] log input gate
-  float* gf = gi + SCAN_CHUNK;           // [CHUNK] log forget gate
+  const bool gate_warp = tid >= nthr;
+  const int col0 = blockIdx.z * CB, lc = (tid % nthr) / R, r = tid % R, col = col0 + lc;
+  const bool live = !gate_warp && col < dv;
+  const int ncol = min(CB, dv - col0);
+  // per buffer: q [ch DP] | k [ch DP] | v [ch CB] | a [ch] | b [ch] | e [ch] | pad [ch]; then the gate warp's scratch (2 ch)
+  const int buf = 2 * ch * DP + ch * CB + 4 * ch;  // (a multiple of 4 floats: rows are read 16 bytes at a time)
+  float* tmp_g = sm + 2 * buf;
+  if (d != DP)
+    for (int x = tid; x < 2 * buf; x += nthr + 32) sm[x] = 0.f;  // the padding of the rows stays zero from here on
   float S[RPT], nn[RPT];
-  float m;
   float* gS = state_S + ((static_cast<size_t>(sd.w) * H + h) * gridDim.z + blockIdx.z) * RPT * nthr;
   float* gn = state_n + (static_cast<size_t>(sd.w) * H + h) * d;
+  float m = 0.f;  // followed by the gate warp only
+#pragma unroll
+  for (int ii = 0; ii < RPT; ++ii) S[ii] = nn[ii] = 0.f;
   if (sd.z > 0) {
-#pragma unroll
-    for (int ii = 0; ii < RPT; ++ii) {
-      S[ii] = gS[ii * nthr + tid];
-      const int i = r + R * ii;
-      nn[ii] = i < d ? gn[i] : 0.f;
-    }
-    m = state_m[sd.w * H + h];
-  } else {
-#pragma unroll
-    for (int ii = 0; ii < RPT; ++ii) S[ii] = nn[ii] = 0.f;
-    m = 0.f;
-  }
-  const float qscale = 1.f / sqrtf(static_cast<float>(d));
-  for (int t0 = 0; t0 < sd.y; t0 += SCAN_CHUNK) {
-    const int cn = min(SCAN_CHUNK, sd.y - t0);
-    __syncthreads();
-    for (int x = tid; x < cn * d; x += nthr) {
-      const long long row = static_cast<long long>(sd.x + t0 + x / d) * ld;
-      qs[x] = to_f(proj[row + q_col0 + h * d + x % d]) * qscale;
-      ks[x] = to_f(proj[row + k_col0 + h * d + x % d]);
-    }
-    for (int x = tid; x < cn * dv; x += nthr) vs[x] = to_f(proj[static_cast<long long>(sd.x + t0 + x / dv) * ld + v_col0 + h * dv + x % dv]);
-    for (int x = tid; x < cn; x += nthr) {
-      const float* gr = gates + static_cast<size_t>(sd.x + t0 + x) * 2 * H;
-      gi[x] = cap * tanhf((gr[h] + bias_i[h]) / cap);
-      gf[x] = logsigmoidf_(cap * tanhf((gr[H + h] + bias_f[h]) / cap));
-    }
-    __syncthreads();
-    for (int x = 0; x < cn; ++x) {
-      const float m_new = fmaxf(gf[x] + m, gi[x]);
-      const float a = expf(gf[x] + m - m_new), b = expf(gi[x] - m_new);
-      m = m_new;
-      const float v = live ? vs[x * dv + col] : 0.f;
-      float po = 0.f, pn = 0.f;
+    if (!gate_warp) {
 #pragma unroll
       for (int ii = 0; ii < RPT; ++ii) {
-        const int i = r + R * ii;
-        const float kk = i < d ? ks[x * d + i] : 0.f, qq = i < d ? qs[x * d + i] : 0.f;
-        const float bk = b * kk;
-        S[ii] = fmaf(a, S[ii], bk * v);
-        nn[ii] = fmaf(a, nn[ii], bk);
-        po = fmaf(S[ii], qq, po);
-        pn = fmaf(nn[ii], qq, pn);
+        S[ii] = gS[ii * nthr + tid];
+        const int i = r * RPT + ii;
+        nn[ii] = i < d ? gn[i] : 0.f;
       }
-      po = lanes_sum<R>(po);
-      pn = lanes_sum<R>(pn);
-      if (live && r == 0) out[static_cast<size_t>(sd.x + t0 + x) * H * dv + h * dv + col] = po / (fmaxf(fabsf(pn), expf(-m)) + 1e-6f);
+    } else {
+      m = state_m[sd.w * H + h];
     }
   }
+  const float qscale = 1.f / sqrtf(static_cast<float>(d));
+  // staged value x = tid + e SCAN_THREADS of a chunk is (token x / d, channel x % d) of q and k and (token x / ncol, column x % ncol) of
+  // v: shifts and masks when the sizes are powers of two, divisions otherwise
+  const int lg_d = (d & (d - 1)) == 0 ? __ffs(d) - 1 : -1, lg_c = (ncol & (ncol - 1)) == 0 ? __ffs(ncol) - 1 : -1;
+  auto split_qk = [&](int x, int& tok, int& c) {
+    if (lg_d >= 0) { tok = x >> lg_d; c = x & (d - 1); } else { tok = x / d; c = x - tok * d; }
+  };
+  auto split_v = [&](int x, int& tok, int& c) {
+    if (lg_c >= 0) { tok = x >> lg_c; c = x & (ncol - 1); } else { tok = x / ncol; c = x - tok * ncol; }
+  };
+  T pq[SCAN_PF], pk[SCAN_PF], pv[SCAN_PF];
+  // the three stages of moving a chunk: global -> registers, registers -> shared buffer, gate recurrence -> shared buffer
+  auto fetch = [&](int t0) {
+    if (gate_warp) return;
+    const int cn = min(ch, sd.y - t0);
+    const T* base = proj + static_cast<long long>(sd.x + t0) * ld + h * d;
+    const T* vbase = proj + static_cast<long long>(sd.x + t0) * ld + v_col0 + h * dv + col0;
 #pragma unroll
-  for (int ii = 0; ii < RPT; ++ii) {
-    gS[ii * nthr + tid] = S[ii];
-    const int i = r + R * ii;
-    if (col == 0 && i < d) gn[i] = nn[ii];  // every column tile carries the same n and m; the first one keeps them
+    for (int e = 0; e < SCAN_PF; ++e) {
+      int tok, c;
+      split_qk(tid + e * nthr, tok, c);
+      if (tok < cn) {
+        pq[e] = base[tok * ld + c + q_col0];
+        pk[e] = base[tok * ld + c + k_col0];
+      }
+      split_v(tid + e * nthr, tok, c);
+      if (tok < cn) pv[e] = vbase[tok * ld + c];
+    }
+  };
+  auto stage = [&](int t0, float* bq) {
+    const int cn = min(ch, sd.y - t0);
+    float* bk = bq + ch * DP;
+    float* bv = bk + ch * DP;
+    if (!gate_warp) {
+#pragma unroll
+      for (int e = 0; e < SCAN_PF; ++e) {
+        int tok, c;
+        split_qk(tid + e * nthr, tok, c);
+        if (tok < cn) {
+          bq[tok * DP + c] = to_f(pq[e]) * qscale;
+          bk[tok * DP + c] = to_f(pk[e]);
+        }
+        split_v(tid + e * nthr, tok, c);
+        if (tok < cn) bv[tok * CB + c] = to_f(pv[e]);
+      }
+      return;
+    }
+    float* ga = bv + ch * CB;
+    float* gb = ga + ch;
+    float* ge = gb + ch;
+    const int lane = tid - nthr;
+    if (lane < cn) {
+      const float* gr = gates + static_cast<size_t>(sd.x + t0 + lane) * 2 * H;
+      tmp_g[lane] = cap * tanhf((gr[h] + bias_i[h]) / cap);
+      tmp_g[ch + lane] = logsigmoidf_(cap * tanhf((gr[H + h] + bias_f[h]) / cap));
+    }
+    __syncwarp();
+    for (int x = 0; x < cn; ++x) {  // every lane walks the recurrence (m stays warp-uniform); lane 0 writes
+      const float ig = tmp_g[x], fg = tmp_g[ch + x];
+      const float m_new = fmaxf(fg + m, ig);
+      const float a = expf(fg + m - m_new), b2 = expf(ig - m_new), e2 = expf(-m_new);
+      m = m_new;
+      if (lane == 0) {
+        ga[x] = a;
+        gb[x] = b2;
+        ge[x] = e2;
+      }
+    }
+    __syncwarp();
+  };
+  __syncthreads();  // the zeros are in place
+  fetch(0);
+  stage(0, sm);
+  __syncthreads();
+  int cur = 0;
+  for (int t0 = 0; t0 < sd.y; t0 += ch, cur ^= 1) {
+    const int cn = min(ch, sd.y - t0);
+    const bool more = t0 + ch < sd.y;
+    if (more) fetch(t0 + ch);
+    if (!gate_warp) {
+      const float* bq = sm + cur * buf + r * RPT;
+      const float* bk = bq + ch * DP;
+      const float* bv = sm + cur * buf + 2 * ch * DP;
+      const float* ga = bv + ch * CB;
+      const float* gb = ga + ch;
+      const float* ge = gb + ch;
+      float* orow = out + static_cast<size_t>(sd.x + t0) * H * dv + h * dv + col;
+#pragma unroll 2
+      for (int x = 0; x < cn; ++x) {
+        const float a = ga[x], b2 = gb[x];
+        const float v = live ? bv[x * CB + lc] : 0.f;
+        float po = 0.f, pn = 0.f;
+#pragma unroll
+        for (int i4 = 0; i4 < RPT; i4 += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(bk + x * DP + i4), q4 = *reinterpret_cast<const float4*>(bq + x * DP + i4);
+          const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float bk2 = b2 * kk[j];
+            S[i4 + j] = fmaf(a, S[i4 + j], bk2 * v);
+            nn[i4 + j] = fmaf(a, nn[i4 + j], bk2);
+            po = fmaf(S[i4 + j], qq[j], po);
+            pn = fmaf(nn[i4 + j], qq[j], pn);
+          }
+        }
+        po = lanes_sum<R>(po);
+        pn = lanes_sum<R>(pn);
+        if (live && r == 0) orow[static_cast<size_t>(x) * H * dv] = po / (fmaxf(fabsf(pn), ge[x]) + 1e-6f);
+      }
+    }
+    if (more) stage(t0 + ch, sm + (cur ^ 1) * buf);
+    __syncthreads();
   }
-  if (tid == 0 && blockIdx.z == 0) state_m[sd.w * H + h] = m;
+  if (!gate_warp) {
+#pragma unroll
+    for (int ii = 0; ii < RPT; ++ii) {
+      gS[ii * nthr + tid] = S[ii];
+      const int i = r * RPT + ii;
+      if (col == 0 && i < d) gn[i] = nn[ii];  // every column tile carries the same n; the first one keeps it
+    }
+  } else if (tid == nthr && blockIdx.z == 0) {
+    state_m[sd.w * H + h] = m;
+  }
 }
 
-// qn / kn fp32 [T, G d] (unit length; q already times d^-1/2), v fp32 [T, H dv], beta_pre fp32 [T, H] (before the sigmoid), a_pre fp32
-// [T, H d] (before dt_bias / softplus).  Head h reads q / k head h / (H / G).  out fp32 [T, H dv].
+// qn / kn fp32 [T, G d] (unit length; q already times d^-1/2), v fp32 [T, H dv], beta fp32 [T, H], decay fp32 [T, H d] (both finished by
+// delta_prepare).  Head h reads q / k head h / (H / G).  out fp32 [T, H dv].
 template <int RPT, int R>
-__global__ void __launch_bounds__(SCAN_THREADS)
-delta_rule_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ v,
-                                       const float* __restrict__ beta_pre, const float* __restrict__ a_pre, const float* __restrict__ A_log,
-                                       const float* __restrict__ dt_bias, const int4* __restrict__ seq_desc, float* __restrict__ state_S,
-                                       float* __restrict__ out, int H, int G, int d, int dv) {
-  extern __shared__ float sm[];
+__global__ void __launch_bounds__(SCAN_THREADS, RPT <= 16 ? 2 : 1)
+delta_rule_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ v, const float* __restrict__ beta,
+                       const float* __restrict__ decay, const int4* __restrict__ seq_desc, float* __restrict__ state_S, float* __restrict__ out,
+                       int H, int G, int d, int dv, int ch) {
+  extern __shared__ __align__(16) float sm[];
+  constexpr int nthr = SCAN_THREADS, CB = nthr / R, DP = R * RPT;
   const int4 sd = seq_desc[blockIdx.x];
   const int h = blockIdx.y, g = h / (H / G), tid = threadIdx.x;
-  constexpr int nthr = SCAN_THREADS;
-  const int col = blockIdx.z * (nthr / R) + tid / R, r = tid % R;
+  const int col0 = blockIdx.z * CB, lc = tid / R, r = tid % R, col = col0 + lc;
   const bool live = col < dv;
-  float* qs = sm;                        // [CHUNK][d]
-  float* ks = qs + SCAN_CHUNK * d;       // [CHUNK][d]
-  float* gs = ks + SCAN_CHUNK * d;       // [CHUNK][d] decays
-  float* vs = gs + SCAN_CHUNK * d;       // [CHUNK][dv]
-  float* bs = vs + SCAN_CHUNK * dv;      // [CHUNK]
+  const int ncol = min(CB, dv - col0);
+  const int buf = 3 * ch * DP + ch * CB + ((ch + 3) & ~3);  // q | k | decay | v | beta (a multiple of 4 floats)
+  if (d != DP)
+    for (int x = tid; x < 2 * buf; x += nthr) sm[x] = 0.f;  // the padding of the rows stays zero from here on
   float S[RPT];
   float* gS = state_S + ((static_cast<size_t>(sd.w) * H + h) * gridDim.z + blockIdx.z) * RPT * nthr;
 #pragma unroll
   for (int ii = 0; ii < RPT; ++ii) S[ii] = sd.z > 0 ? gS[ii * nthr + tid] : 0.f;
-  const float rate = expf(A_log[h]);
-  for (int t0 = 0; t0 < sd.y; t0 += SCAN_CHUNK) {
-    const int cn = min(SCAN_CHUNK, sd.y - t0);
-    __syncthreads();
-    for (int x = tid; x < cn * d; x += nthr) {
-      const size_t row = static_cast<size_t>(sd.x + t0 + x / d);
-      const int i = x % d;
-      qs[x] = qn[row * G * d + g * d + i];
-      ks[x] = kn[row * G * d + g * d + i];
-      gs[x] = expf(-rate * softplusf_(a_pre[row * H * d + h * d + i] + dt_bias[h * d + i]));
+  const int lg_d = (d & (d - 1)) == 0 ? __ffs(d) - 1 : -1, lg_c = (ncol & (ncol - 1)) == 0 ? __ffs(ncol) - 1 : -1;
+  auto split_qk = [&](int x, int& tok, int& c) {
+    if (lg_d >= 0) { tok = x >> lg_d; c = x & (d - 1); } else { tok = x / d; c = x - tok * d; }
+  };
+  auto split_v = [&](int x, int& tok, int& c) {
+    if (lg_c >= 0) { tok = x >> lg_c; c = x & (ncol - 1); } else { tok = x / ncol; c = x - tok * ncol; }
+  };
+  float pq[SCAN_PF], pk[SCAN_PF], pg[SCAN_PF], pv[SCAN_PF], pb = 0.f;
+  auto fetch = [&](int t0) {
+    const int cn = min(ch, sd.y - t0);
+    const size_t row0 = static_cast<size_t>(sd.x + t0);
+    const float *q0 = qn + row0 * G * d + g * d, *k0 = kn + row0 * G * d + g * d, *g0 = decay + row0 * H * d + h * d,
+                *v0 = v + row0 * H * dv + h * dv + col0;
+#pragma unroll
+    for (int e = 0; e < SCAN_PF; ++e) {
+      int tok, c;
+      split_qk(tid + e * nthr, tok, c);
+      if (tok < cn) {
+        pq[e] = q0[tok * G * d + c];
+        pk[e] = k0[tok * G * d + c];
+        pg[e] = g0[tok * H * d + c];
+      }
+      split_v(tid + e * nthr, tok, c);
+      if (tok < cn) pv[e] = v0[tok * H * dv + c];
     }
-    for (int x = tid; x < cn * dv; x += nthr) vs[x] = v[static_cast<size_t>(sd.x + t0 + x / dv) * H * dv + h * dv + x % dv];
-    for (int x = tid; x < cn; x += nthr) bs[x] = sigmoidf_(beta_pre[static_cast<size_t>(sd.x + t0 + x) * H + h]);
-    __syncthreads();
+    if (tid < cn) pb = beta[(row0 + tid) * H + h];
+  };
+  auto stage = [&](int t0, float* bq) {
+    const int cn = min(ch, sd.y - t0);
+    float* bk = bq + ch * DP;
+    float* bg = bk + ch * DP;
+    float* bv = bg + ch * DP;
+    float* bb = bv + ch * CB;
+#pragma unroll
+    for (int e = 0; e < SCAN_PF; ++e) {
+      int tok, c;
+      split_qk(tid + e * nthr, tok, c);
+      if (tok < cn) {
+        bq[tok * DP + c] = pq[e];
+        bk[tok * DP + c] = pk[e];
+        bg[tok * DP + c] = pg[e];
+      }
+      split_v(tid + e * nthr, tok, c);
+      if (tok < cn) bv[tok * CB + c] = pv[e];
+    }
+    if (tid < cn) bb[tid] = pb;
+  };
+  __syncthreads();  // the zeros are in place
+  fetch(0);
+  stage(0, sm);
+  __syncthreads();
+  int cur = 0;
+  for (int t0 = 0; t0 < sd.y; t0 += ch, cur ^= 1) {
+    const int cn = min(ch, sd.y - t0);
+    const bool more = t0 + ch < sd.y;
+    if (more) fetch(t0 + ch);
+    const float* bq = sm + cur * buf + r * RPT;
+    const float* bk = bq + ch * DP;
+    const float* bg = bk + ch * DP;
+    const float* bv = sm + cur * buf + 3 * ch * DP;
+    const float* bb = bv + ch * CB;
+    float* orow = out + static_cast<size_t>(sd.x + t0) * H * dv + h * dv + col;
     for (int x = 0; x < cn; ++x) {
-      float ps = 0.f;
+      float ps0 = 0.f, ps1 = 0.f;
+      float kk[RPT];
 #pragma unroll
-      for (int ii = 0; ii < RPT; ++ii) {
-        const int i = r + R * ii;
-        if (i < d) {
-          S[ii] *= gs[x * d + i];
-          ps = fmaf(S[ii], ks[x * d + i], ps);
-        }
+      for (int i4 = 0; i4 < RPT; i4 += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(bk + x * DP + i4), g4 = *reinterpret_cast<const float4*>(bg + x * DP + i4);
+        kk[i4] = k4.x; kk[i4 + 1] = k4.y; kk[i4 + 2] = k4.z; kk[i4 + 3] = k4.w;
+        S[i4] *= g4.x; S[i4 + 1] *= g4.y; S[i4 + 2] *= g4.z; S[i4 + 3] *= g4.w;  // padded rows: decay 0 on a state of 0
+        ps0 = fmaf(S[i4], k4.x, ps0); ps1 = fmaf(S[i4 + 1], k4.y, ps1);
+        ps0 = fmaf(S[i4 + 2], k4.z, ps0); ps1 = fmaf(S[i4 + 3], k4.w, ps1);
       }
-      ps = lanes_sum<R>(ps);
-      const float u = live ? bs[x] * (vs[x * dv + col] - ps) : 0.f;
-      float po = 0.f;
+      const float ps = lanes_sum<R>(ps0 + ps1);
+      const float u = live ? bb[x] * (bv[x * CB + lc] - ps) : 0.f;
+      float po0 = 0.f, po1 = 0.f;
 #pragma unroll
-      for (int ii = 0; ii < RPT; ++ii) {
-        const int i = r + R * ii;
-        if (i < d) {
-          S[ii] = fmaf(ks[x * d + i], u, S[ii]);
-          po = fmaf(S[ii], qs[x * d + i], po);
-        }
+      for (int i4 = 0; i4 < RPT; i4 += 4) {
+        const float4 q4 = *reinterpret_cast<const float4*>(bq + x * DP + i4);
+        S[i4] = fmaf(kk[i4], u, S[i4]); S[i4 + 1] = fmaf(kk[i4 + 1], u, S[i4 + 1]);
+        S[i4 + 2] = fmaf(kk[i4 + 2], u, S[i4 + 2]); S[i4 + 3] = fmaf(kk[i4 + 3], u, S[i4 + 3]);
+        po0 = fmaf(S[i4], q4.x, po0); po1 = fmaf(S[i4 + 1], q4.y, po1);
+        po0 = fmaf(S[i4 + 2], q4.z, po0); po1 = fmaf(S[i4 + 3], q4.w, po1);
       }
-      po = lanes_sum<R>(po);
-      if (live && r == 0) out[static_cast<size_t>(sd.x + t0 + x) * H * dv + h * dv + col] = po;
+      const float po = lanes_sum<R>(po0 + po1);
+      if (live && r == 0) orow[static_cast<size_t>(x) * H * dv] = po;
     }
+    if (more) stage(t0 + ch, sm + (cur ^ 1) * buf);
+    __syncthreads();
   }
 #pragma unroll
   for (int ii = 0; ii < RPT; ++ii) gS[ii * nthr + tid] = S[ii];
@@ -417,42 +557,50 @@ delta_rule_scan_kernel(const float* __restrict__ qn, const float* __restrict__ k
 
 // One block per token.  proj row holds the q [G d], k [G d] and v [H dv] projections at q_col0 / k_col0 / v_col0; the kept rows of the
 // sequence are [taps - 1, 2 G d + H dv] (q | k | v channels).  Each goes through its short convolution and silu; q and k are then made unit
-// vectors per head (x / sqrt(sum x^2 + 1e-6)), q also times d^-1/2.  Outputs fp32.
+// vectors per head (x / sqrt(sum x^2 + 1e-6)), q also times d^-1/2: a warp takes a head at a time, so the sums need no atomics.  The same
+// pass finishes what else the scan reads per token: a_pre [T, H d] becomes the decay exp(-exp(A_log) softplus(a_pre + dt_bias)) and
+// beta_pre [T, H] becomes sigmoid(beta_pre), both in place.  Outputs fp32.
 template <typename T>
 __global__ void delta_prepare_kernel(const T* __restrict__ proj, long long ld, int q_col0, int k_col0, int v_col0, const float* __restrict__ conv_q,
                                      const float* __restrict__ conv_k, const float* __restrict__ conv_v, const T* __restrict__ state,
                                      const int4* __restrict__ seq_desc, const int* __restrict__ tok_seq, float* __restrict__ qn,
-                                     float* __restrict__ kn, float* __restrict__ vo, int G, int H, int d, int dv, int taps) {
+                                     float* __restrict__ kn, float* __restrict__ vo, float* __restrict__ a_pre, float* __restrict__ beta_pre,
+                                     const float* __restrict__ A_log, const float* __restrict__ dt_bias, int G, int H, int d, int dv, int taps) {
   extern __shared__ float sm[];
   const int t = blockIdx.x;
   const int nqk = G * d, nv = H * dv, C = 2 * nqk + nv;
-  float* y = sm;             // [2 G d]: q then k
-  float* ss = sm + 2 * nqk;  // [2 G] sums of squares per head
+  float* y = sm;  // [2 G d]: q then k
   const int4 sd = seq_desc[tok_seq[t]];
   const int i = t - sd.x;
   const T* st = state + static_cast<size_t>(sd.w) * (taps - 1) * C;
   const T* u0 = proj + static_cast<long long>(sd.x) * ld;
-  for (int c = threadIdx.x; c < 2 * G; c += blockDim.x) ss[c] = 0.f;
-  __syncthreads();
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    const int which = c < nqk ? 0 : (c < 2 * nqk ? 1 : 2);
-    const int cc = c - (which == 0 ? 0 : (which == 1 ? nqk : 2 * nqk));
-    const int col0 = which == 0 ? q_col0 : (which == 1 ? k_col0 : v_col0);
-    const float* w = (which == 0 ? conv_q : (which == 1 ? conv_k : conv_v)) + static_cast<size_t>(cc) * taps;
-    const float val = siluf_(conv_at(u0 + col0 + cc, ld, st + c, C, w, taps, i, sd.z));
-    if (which == 2) vo[static_cast<size_t>(t) * nv + cc] = val;
-    else {
-      y[c] = val;
-      atomicAdd(&ss[which * G + cc / d], val * val);
-    }
-  }
-  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const float qscale = 1.f / sqrtf(static_cast<float>(d));
-  for (int c = threadIdx.x; c < 2 * nqk; c += blockDim.x) {
-    const int which = c < nqk ? 0 : 1, cc = c - which * nqk;
-    const float inv = 1.f / sqrtf(ss[which * G + cc / d] + 1e-6f);
-    if (which == 0) qn[static_cast<size_t>(t) * nqk + cc] = y[c] * inv * qscale;
-    else kn[static_cast<size_t>(t) * nqk + cc] = y[c] * inv;
+  for (int hh = warp; hh < 2 * G; hh += nw) {  // head hh of (q heads | k heads)
+    const int which = hh < G ? 0 : 1;
+    const int c0 = hh * d;  // first channel of the head among the 2 G d
+    const int col0 = (which ? k_col0 : q_col0) + (hh - which * G) * d;
+    const float* w = (which ? conv_k : conv_q) + static_cast<size_t>(hh - which * G) * d * taps;
+    float ss = 0.f;
+    for (int c = lane; c < d; c += 32) {
+      const float val = siluf_(conv_at(u0 + col0 + c, ld, st + c0 + c, C, w + static_cast<size_t>(c) * taps, taps, i, sd.z));
+      y[c0 + c] = val;
+      ss += val * val;
+    }
+    ss = warp_sum(ss);
+    const float inv = (which ? 1.f : qscale) / sqrtf(ss + 1e-6f);
+    float* dst = (which ? kn : qn) + static_cast<size_t>(t) * nqk + (hh - which * G) * d;
+    for (int c = lane; c < d; c += 32) dst[c] = y[c0 + c] * inv;  // each lane re-reads what it wrote
+  }
+  for (int c = threadIdx.x; c < nv; c += blockDim.x)
+    vo[static_cast<size_t>(t) * nv + c] = siluf_(conv_at(u0 + v_col0 + c, ld, st + 2 * nqk + c, C, conv_v + static_cast<size_t>(c) * taps, taps, i, sd.z));
+  for (int c = threadIdx.x; c < H * d; c += blockDim.x) {
+    float* a = a_pre + static_cast<size_t>(t) * H * d + c;
+    *a = expf(-expf(A_log[c / d]) * softplusf_(*a + dt_bias[c]));
+  }
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float* bp = beta_pre + static_cast<size_t>(t) * H + c;
+    *bp = sigmoidf_(*bp);
   }
 }
 
@@ -479,10 +627,10 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
 using namespace dsb;
 using namespace dsb::recur;
 
-// Lanes per column (R), rows per thread (RPT, rounded up to 8 / 16 / 32 / 64) and column tiles of a d x dv state: about 8 rows per thread
-// (a short dependent chain per token); a block of SCAN_THREADS threads then covers SCAN_THREADS / R columns.
-static bool scan_shape(int d, int dv, int* R, int* RPT, int* tiles) {
-  if (d < 1 || dv < 1) return false;
+// Lanes per column (R), rows per thread (RPT, rounded up to 8 / 16 / 32 / 64), column tiles of a d x dv state and tokens per staged
+// chunk: about 8 rows per thread (a short dependent chain per token); a block of SCAN_THREADS threads then covers SCAN_THREADS / R columns.
+static bool scan_shape(int d, int dv, int* R, int* RPT, int* tiles, int* chunk = nullptr) {
+  if (d < 1 || dv < 1 || d > SCAN_PF * SCAN_THREADS) return false;
   int r = 1;
   while (r < 32 && (d + r - 1) / r > 8) r <<= 1;
   const int need = (d + r - 1) / r;
@@ -492,6 +640,11 @@ static bool scan_shape(int d, int dv, int* R, int* RPT, int* tiles) {
   *R = r;
   *RPT = rpt;
   *tiles = (dv + cols - 1) / cols;
+  if (chunk) {
+    int ch = 16;
+    while (ch > 1 && (ch * d > SCAN_PF * SCAN_THREADS || ch * cols > SCAN_PF * SCAN_THREADS)) ch >>= 1;
+    *chunk = ch;
+  }
   return rpt <= 64;
 }
 
@@ -591,23 +744,31 @@ DSB_EXPORT int dsb200_matrix_memory_scan(const void* proj, long long ld, int q_c
                                          float* state_n, float* state_m, float* out, int n_seqs, int H, int d, int dv, int dtype,
                                          cudaStream_t stream) {
   if (n_seqs == 0) return DSB_OK;
-  int R, RPT, tiles;
-  DSB_REQUIRE(scan_shape(d, dv, &R, &RPT, &tiles), "matrix_memory_scan: a %d x %d state per head is not supported", d, dv);
-  const int threads = SCAN_THREADS;
-  const size_t smem = (static_cast<size_t>(SCAN_CHUNK) * (2 * d + dv + 2)) * sizeof(float);
-  DSB_REQUIRE(smem <= 48 * 1024, "matrix_memory_scan: head sizes %d / %d do not fit shared memory", d, dv);
+  int R, RPT, tiles, ch;
+  DSB_REQUIRE(scan_shape(d, dv, &R, &RPT, &tiles, &ch), "matrix_memory_scan: a %d x %d state per head is not supported", d, dv);
+  const int threads = SCAN_THREADS + 32;
+  const size_t smem = (2 * static_cast<size_t>(2 * ch * R * RPT + ch * (SCAN_THREADS / R) + 4 * ch) + 2 * ch) * sizeof(float);
+  DSB_REQUIRE(smem <= 200 * 1024, "matrix_memory_scan: head sizes %d / %d do not fit shared memory", d, dv);
   const dim3 grid(n_seqs, H, tiles);
   bool launched = false;
 #define CALL(RPTv, Rv)                                                                                                                    \
   do {                                                                                                                                    \
     if (dtype == 0)                                                                                                                       \
+    {                                                                                                                                     \
+      if (smem > 48 * 1024)                                                                                                               \
+        DSB_CHECK_CUDA(cudaFuncSetAttribute(matrix_memory_scan_kernel<bf16, RPTv, Rv>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
       matrix_memory_scan_kernel<bf16, RPTv, Rv><<<grid, threads, smem, stream>>>((const bf16*)proj, ld, q_col0, k_col0, v_col0, gates, bias_i, \
                                                                                  bias_f, cap, (const int4*)seq_desc, state_S, state_n,    \
-                                                                                 state_m, out, H, d, dv);                                 \
+                                                                                 state_m, out, H, d, dv, ch);                             \
+    }                                                                                                                                     \
     else                                                                                                                                  \
+    {                                                                                                                                     \
+      if (smem > 48 * 1024)                                                                                                               \
+        DSB_CHECK_CUDA(cudaFuncSetAttribute(matrix_memory_scan_kernel<float, RPTv, Rv>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
       matrix_memory_scan_kernel<float, RPTv, Rv><<<grid, threads, smem, stream>>>((const float*)proj, ld, q_col0, k_col0, v_col0, gates,      \
                                                                                   bias_i, bias_f, cap, (const int4*)seq_desc, state_S,    \
-                                                                                  state_n, state_m, out, H, d, dv);                       \
+                                                                                  state_n, state_m, out, H, d, dv, ch);                   \
+    }                                                                                                                                     \
   } while (0)
   SCAN_DISPATCH_ALL(CALL);
 #undef CALL
@@ -619,19 +780,22 @@ DSB_EXPORT int dsb200_matrix_memory_scan(const void* proj, long long ld, int q_c
 // Inputs of the delta-rule scan from the fused projection proj [T, ld] (dtype 0 = bf16, 1 = fp32): q [G d] at q_col0, k [G d] at k_col0, v
 // [H dv] at v_col0, each through its short convolution (weights fp32 [channels, taps]; earlier rows from the batch or from `state`
 // [slots, taps - 1, 2 G d + H dv]) and silu; q and k then scaled to unit length per head (x / sqrt(sum x^2 + 1e-6)), q also by d^-1/2.
-// qn, kn fp32 [T, G d]; vo fp32 [T, H dv].  Call dsb200_conv_state_update (three column ranges) afterwards.
+// qn, kn fp32 [T, G d]; vo fp32 [T, H dv].  In place: a_pre fp32 [T, H d] <- exp(-exp(A_log[h]) softplus(a_pre + dt_bias)) (the decays) and
+// beta_pre fp32 [T, H] <- sigmoid(beta_pre).  Call dsb200_conv_state_update afterwards.
 DSB_EXPORT int dsb200_delta_prepare(const void* proj, long long ld, int q_col0, int k_col0, int v_col0, const float* conv_q, const float* conv_k,
                                     const float* conv_v, const void* state, const int* seq_desc, const int* tok_seq, float* qn, float* kn,
-                                    float* vo, int n_tokens, int G, int H, int d, int dv, int taps, int dtype, cudaStream_t stream) {
+                                    float* vo, float* a_pre, float* beta_pre, const float* A_log, const float* dt_bias, int n_tokens, int G, int H,
+                                    int d, int dv, int taps, int dtype, cudaStream_t stream) {
   if (n_tokens == 0) return DSB_OK;
-  const size_t smem = (2 * static_cast<size_t>(G) * d + 2 * G) * sizeof(float);
+  const size_t smem = 2 * static_cast<size_t>(G) * d * sizeof(float);
   DSB_REQUIRE(smem <= 200 * 1024, "delta_prepare: 2 G d = %d does not fit shared memory", 2 * G * d);
   const int block = 2 * G * d + H * dv >= 2048 ? 512 : 256;
 #define LAUNCH(T)                                                                                                                       \
   do {                                                                                                                                  \
     if (smem > 48 * 1024) DSB_CHECK_CUDA(cudaFuncSetAttribute(delta_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
     delta_prepare_kernel<T><<<n_tokens, block, smem, stream>>>((const T*)proj, ld, q_col0, k_col0, v_col0, conv_q, conv_k, conv_v,        \
-                                                               (const T*)state, (const int4*)seq_desc, tok_seq, qn, kn, vo, G, H, d, dv, taps); \
+                                                               (const T*)state, (const int4*)seq_desc, tok_seq, qn, kn, vo, a_pre, beta_pre,  \
+                                                               A_log, dt_bias, G, H, d, dv, taps);                                        \
   } while (0)
   if (dtype == 0) LAUNCH(bf16);
   else LAUNCH(float);
@@ -641,24 +805,26 @@ DSB_EXPORT int dsb200_delta_prepare(const void* proj, long long ld, int q_col0, 
 }
 
 // Gated delta rule with one decay per head and key channel, per sequence and head over the new tokens in order:
-//   g = exp(-exp(A_log[h]) softplus(a_pre[t, h, :] + dt_bias[h, :]));  S <- diag(g) S;  u = sigmoid(beta_pre[t, h]) (v - S^T k);
-//   S <- S + k u^T;  out = S^T q
-// qn, kn fp32 [T, G d] (head h reads q / k head h / (H / G)), v fp32 [T, H dv], beta_pre fp32 [T, H], a_pre fp32 [T, H d]; out fp32 [T, H dv];
-// state_S [slots, H, dsb200_scan_state_floats(d, dv)] fp32; a sequence at position 0 starts from zeros.
-DSB_EXPORT int dsb200_delta_rule_scan(const float* qn, const float* kn, const float* v, const float* beta_pre, const float* a_pre,
-                                      const float* A_log, const float* dt_bias, const int* seq_desc, float* state_S, float* out, int n_seqs,
-                                      int H, int G, int d, int dv, cudaStream_t stream) {
+//   S <- diag(decay[t, h, :]) S;  u = beta[t, h] (v - S^T k);  S <- S + k u^T;  out = S^T q
+// qn, kn fp32 [T, G d] (head h reads q / k head h / (H / G)), v fp32 [T, H dv], beta fp32 [T, H], decay fp32 [T, H d] (as dsb200_delta_prepare
+// leaves them); out fp32 [T, H dv]; state_S [slots, H, dsb200_scan_state_floats(d, dv)] fp32; a sequence at position 0 starts from zeros.
+DSB_EXPORT int dsb200_delta_rule_scan(const float* qn, const float* kn, const float* v, const float* beta, const float* decay, const int* seq_desc,
+                                      float* state_S, float* out, int n_seqs, int H, int G, int d, int dv, cudaStream_t stream) {
   if (n_seqs == 0) return DSB_OK;
-  int R, RPT, tiles;
-  DSB_REQUIRE(H % G == 0 && scan_shape(d, dv, &R, &RPT, &tiles), "delta_rule_scan: heads %d / %d, a %d x %d state per head is not supported", H, G, d, dv);
+  int R, RPT, tiles, ch;
+  DSB_REQUIRE(H % G == 0 && scan_shape(d, dv, &R, &RPT, &tiles, &ch), "delta_rule_scan: heads %d / %d, a %d x %d state per head is not supported", H, G, d,
+              dv);
   const int threads = SCAN_THREADS;
-  const size_t smem = (static_cast<size_t>(SCAN_CHUNK) * (3 * d + dv + 1)) * sizeof(float);
-  DSB_REQUIRE(smem <= 48 * 1024, "delta_rule_scan: head sizes %d / %d do not fit shared memory", d, dv);
+  const size_t smem = 2 * static_cast<size_t>(3 * ch * R * RPT + ch * (SCAN_THREADS / R) + ((ch + 3) & ~3)) * sizeof(float);
+  DSB_REQUIRE(smem <= 200 * 1024, "delta_rule_scan: head sizes %d / %d do not fit shared memory", d, dv);
   const dim3 grid(n_seqs, H, tiles);
   bool launched = false;
-#define CALL(RPTv, Rv)                                                                                                                       \
-  delta_rule_scan_kernel<RPTv, Rv><<<grid, threads, smem, stream>>>(qn, kn, v, beta_pre, a_pre, A_log, dt_bias, (const int4*)seq_desc, state_S, \
-                                                                    out, H, G, d, dv)
+#define CALL(RPTv, Rv)                                                                                                                         \
+  do {                                                                                                                                         \
+    if (smem > 48 * 1024)                                                                                                                      \
+      DSB_CHECK_CUDA(cudaFuncSetAttribute(delta_rule_scan_kernel<RPTv, Rv>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));            \
+    delta_rule_scan_kernel<RPTv, Rv><<<grid, threads, smem, stream>>>(qn, kn, v, beta, decay, (const int4*)seq_desc, state_S, out, H, G, d, dv, ch); \
+  } while (0)
   SCAN_DISPATCH_ALL(CALL);
 #undef CALL
   DSB_REQUIRE(launched, "delta_rule_scan: no kernel for %d rows per thread x %d lanes", RPT, R);

@@ -457,8 +457,8 @@ native.register_sigs({
     "dsb200_conv_state_update": "p l i p ii p iii i p",
     "dsb200_window_attention": "p l p ppp ii p l iiiiii ff i p",
     "dsb200_matrix_memory_scan": "p l iii ppp f p ppp p iiii i p",
-    "dsb200_delta_prepare": "p l iii ppp p pp ppp iiiiii i p",
-    "dsb200_delta_rule_scan": "ppppp pp p pp iiiii p",
+    "dsb200_delta_prepare": "p l iii ppp p pp ppp pppp iiiiii i p",
+    "dsb200_delta_rule_scan": "ppppp p pp iiiii p",
     "dsb200_head_norm_gate": "pp i p l p l iii ff i p",
 }, restype_long=("dsb200_scan_state_floats", ))
 
@@ -549,29 +549,34 @@ def matrix_memory_scan(proj, q_col0, k_col0, v_col0, gates, bias_i, bias_f, cap,
     return out
 
 
-def delta_prepare(proj, q_col0, k_col0, v_col0, conv_q, conv_k, conv_v, state, seq_desc, tok_seq, G, H, d, dv, taps):
+def delta_prepare(proj, q_col0, k_col0, v_col0, conv_q, conv_k, conv_v, state, seq_desc, tok_seq, a_pre, beta_pre, A_log, dt_bias, G, H, d, dv, taps):
     """Short convolution + silu of the q / k / v projections, q and k to unit length per head (q also times d^-1/2) ->
-    fp32 (q [T, G d], k [T, G d], v [T, H dv]).  Follow with `conv_state_update`."""
+    fp32 (q [T, G d], k [T, G d], v [T, H dv]).  In place: a_pre fp32 [T, H d] becomes the decays exp(-exp(A_log) softplus(a_pre + dt_bias))
+    and beta_pre fp32 [T, H] becomes sigmoid(beta_pre).  Follow with `conv_state_update`."""
     T = proj.shape[0]
     assert proj.stride(1) == 1
+    for t, shape in ((a_pre, (T, H * d)), (beta_pre, (T, H))):
+        assert t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape) == shape
     qn = torch.empty(T, G * d, dtype=torch.float32, device=proj.device)
     kn = torch.empty(T, G * d, dtype=torch.float32, device=proj.device)
     vo = torch.empty(T, H * dv, dtype=torch.float32, device=proj.device)
     native.check(native.lib().dsb200_delta_prepare(native.ptr(proj), proj.stride(0), q_col0, k_col0, v_col0, native.ptr(conv_q), native.ptr(conv_k),
                                                    native.ptr(conv_v), native.ptr(state), native.ptr(seq_desc), native.ptr(tok_seq), native.ptr(qn),
-                                                   native.ptr(kn), native.ptr(vo), T, G, H, d, dv, taps, _dt(proj), native.stream_ptr()))
+                                                   native.ptr(kn), native.ptr(vo), native.ptr(a_pre), native.ptr(beta_pre), native.ptr(A_log),
+                                                   native.ptr(dt_bias), T, G, H, d, dv, taps, _dt(proj), native.stream_ptr()))
     return qn, kn, vo
 
 
-def delta_rule_scan(qn, kn, v, beta_pre, a_pre, A_log, dt_bias, seq_desc, n_seqs, state_S, H, G, d, dv):
-    """Gated delta rule with per-channel decays over every sequence's new tokens -> fp32 [T, H dv] read-outs."""
+def delta_rule_scan(qn, kn, v, beta, decay, seq_desc, n_seqs, state_S, H, G, d, dv):
+    """Gated delta rule with per-channel decays over every sequence's new tokens -> fp32 [T, H dv] read-outs.  beta [T, H] and decay
+    [T, H d] as `delta_prepare` leaves them."""
     T = qn.shape[0]
-    for t in (qn, kn, v, beta_pre, a_pre):
+    for t in (qn, kn, v, beta, decay):
         assert t.dtype == torch.float32 and t.is_contiguous()
     out = torch.empty(T, H * dv, dtype=torch.float32, device=qn.device)
-    native.check(native.lib().dsb200_delta_rule_scan(native.ptr(qn), native.ptr(kn), native.ptr(v), native.ptr(beta_pre), native.ptr(a_pre),
-                                                     native.ptr(A_log), native.ptr(dt_bias), native.ptr(seq_desc), native.ptr(state_S),
-                                                     native.ptr(out), n_seqs, H, G, d, dv, native.stream_ptr()))
+    native.check(native.lib().dsb200_delta_rule_scan(native.ptr(qn), native.ptr(kn), native.ptr(v), native.ptr(beta), native.ptr(decay),
+                                                     native.ptr(seq_desc), native.ptr(state_S), native.ptr(out), n_seqs, H, G, d, dv,
+                                                     native.stream_ptr()))
     return out
 
 

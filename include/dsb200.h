@@ -498,19 +498,20 @@ int dsb200_matrix_memory_scan(const void* proj, long long ld, int q_col0, int k_
 /* Inputs of the delta-rule scan from the fused projection proj [T, ld] (dtype 0 = bf16, 1 = fp32): q [G d] at q_col0, k [G d] at k_col0, v
  * [H dv] at v_col0, each through its short convolution (weights fp32 [channels, taps]; earlier rows from the batch or from `state`
  * [slots, taps - 1, 2 G d + H dv]) and silu; q and k then scaled to unit length per head (x / sqrt(sum x^2 + 1e-6)), q also by d^-1/2.
- * qn, kn fp32 [T, G d]; vo fp32 [T, H dv].  Call dsb200_conv_state_update (three column ranges) afterwards. */
+ * qn, kn fp32 [T, G d]; vo fp32 [T, H dv].  In place: a_pre fp32 [T, H d] <- exp(-exp(A_log[h]) softplus(a_pre + dt_bias)) (the decays) and
+ * beta_pre fp32 [T, H] <- sigmoid(beta_pre).  Call dsb200_conv_state_update afterwards. */
 int dsb200_delta_prepare(const void* proj, long long ld, int q_col0, int k_col0, int v_col0, const float* conv_q,
                          const float* conv_k, const float* conv_v, const void* state, const int* seq_desc,
-                         const int* tok_seq, float* qn, float* kn, float* vo, int n_tokens, int G, int H, int d, int dv,
-                         int taps, int dtype, dsb200_stream_t stream);
+                         const int* tok_seq, float* qn, float* kn, float* vo, float* a_pre, float* beta_pre,
+                         const float* A_log, const float* dt_bias, int n_tokens, int G, int H, int d, int dv, int taps,
+                         int dtype, dsb200_stream_t stream);
 /* Gated delta rule with one decay per head and key channel, per sequence and head over the new tokens in order:
- *   g = exp(-exp(A_log[h]) softplus(a_pre[t, h, :] + dt_bias[h, :]));  S <- diag(g) S;  u = sigmoid(beta_pre[t, h]) (v - S^T k);
- *   S <- S + k u^T;  out = S^T q
- * qn, kn fp32 [T, G d] (head h reads q / k head h / (H / G)), v fp32 [T, H dv], beta_pre fp32 [T, H], a_pre fp32 [T, H d]; out fp32 [T, H dv];
- * state_S [slots, H, dsb200_scan_state_floats(d, dv)] fp32; a sequence at position 0 starts from zeros. */
-int dsb200_delta_rule_scan(const float* qn, const float* kn, const float* v, const float* beta_pre, const float* a_pre,
-                           const float* A_log, const float* dt_bias, const int* seq_desc, float* state_S, float* out,
-                           int n_seqs, int H, int G, int d, int dv, dsb200_stream_t stream);
+ *   S <- diag(decay[t, h, :]) S;  u = beta[t, h] (v - S^T k);  S <- S + k u^T;  out = S^T q
+ * qn, kn fp32 [T, G d] (head h reads q / k head h / (H / G)), v fp32 [T, H dv], beta fp32 [T, H], decay fp32 [T, H d] (as dsb200_delta_prepare
+ * leaves them); out fp32 [T, H dv]; state_S [slots, H, dsb200_scan_state_floats(d, dv)] fp32; a sequence at position 0 starts from zeros. */
+int dsb200_delta_rule_scan(const float* qn, const float* kn, const float* v, const float* beta, const float* decay,
+                           const int* seq_desc, float* state_S, float* out, int n_seqs, int H, int G, int d, int dv,
+                           dsb200_stream_t stream);
 /* out[t, h dv + c] = o[t, h, c] / sqrt(mean_c o[t, h, :]^2 + eps) * w[h * w_stride + c] * sigmoid(gate[t, h dv + c]) * mult.  o fp32
  * [T, H dv]; w fp32 (w_stride = dv: one weight row per head, 0: one row shared by the heads); gate [T, gate_ld] and out [T, out_ld] in the
  * activation dtype (0 = bf16, 1 = fp32). */
