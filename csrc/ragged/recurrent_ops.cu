@@ -174,15 +174,16 @@ __global__ void window_qk_prepare_kernel(const T* __restrict__ proj, long long l
   sk = block_sum(sk, red);  // (the barriers inside also publish y, cs, sn)
   const float inv_q = 1.f / sqrtf(sq / static_cast<float>(nq) + eps), inv_k = 1.f / sqrtf(sk / static_cast<float>(nk) + eps);
   T* qrow = q_out + static_cast<long long>(t) * q_ld;
-  for (int pr = threadIdx.x; pr < C / 2; pr += blockDim.x) {
-    const int c = 2 * pr;
-    const bool is_q = c < nq;
+  const int hp = (d + 1) / 2;  // pairs (2p, 2p + 1) per head; the last one of an odd head size has no second entry
+  for (int pr = threadIdx.x; pr < (H + G) * hp; pr += blockDim.x) {
+    const int head = pr / hp, within = 2 * (pr - head * hp);
+    const int c = head * d + within;
+    const bool is_q = c < nq, two = within + 1 < d;
     const int cc = is_q ? c : c - nq;
     const float inv = is_q ? inv_q : inv_k;
     const float* nw = is_q ? norm_q : norm_k;
-    float a = y[c] * inv * nw[cc], b = y[c + 1] * inv * nw[cc + 1];
-    const int within = cc % d;
-    if (within < rot_dims) {
+    float a = y[c] * inv * nw[cc], b = two ? y[c + 1] * inv * nw[cc + 1] : 0.f;
+    if (within + 1 < rot_dims) {
       const float co = cs[within >> 1], si = sn[within >> 1];
       const float ra = a * co - b * si, rb = b * co + a * si;
       a = ra;
@@ -190,7 +191,7 @@ __global__ void window_qk_prepare_kernel(const T* __restrict__ proj, long long l
     }
     T* dst = is_q ? qrow : krow;
     dst[cc] = from_f<T>(a);
-    dst[cc + 1] = from_f<T>(b);
+    if (two) dst[cc + 1] = from_f<T>(b);
   }
 }
 
@@ -677,7 +678,7 @@ DSB_EXPORT int dsb200_window_qk_prepare(const void* proj, long long ld, int q_co
                                         long long q_ld, const double* freq, int n_tokens, int H, int G, int d, int taps, int rot_dims, float eps,
                                         int dtype, cudaStream_t stream) {
   if (n_tokens == 0) return DSB_OK;
-  DSB_REQUIRE(H >= 1 && G >= 1 && H % G == 0 && d % 2 == 0 && rot_dims % 2 == 0 && rot_dims <= d && taps >= 1,
+  DSB_REQUIRE(H >= 1 && G >= 1 && H % G == 0 && d >= 1 && rot_dims % 2 == 0 && rot_dims <= d && taps >= 1,
               "window_qk_prepare: heads %d / %d, head size %d, rotated %d, taps %d", H, G, d, rot_dims, taps);
   const size_t smem = (static_cast<size_t>(H + G) * d + rot_dims) * sizeof(float);
   DSB_REQUIRE(smem <= 200 * 1024, "window_qk_prepare: (H + G) d = %d does not fit shared memory", (H + G) * d);

@@ -117,8 +117,8 @@ class DSWindowedAttentionConfig(DSModuleConfig):
     def _consistent(self):
         if self.n_heads_q <= 0 or self.n_heads_kv <= 0 or self.n_heads_q % self.n_heads_kv != 0:
             raise ValueError(f"n_heads_q ({self.n_heads_q}) must be a positive multiple of n_heads_kv ({self.n_heads_kv})")
-        if self.head_size <= 0 or self.head_size % 2 != 0:
-            raise ValueError(f"head_size must be positive and even, got {self.head_size}")
+        if self.head_size <= 0:
+            raise ValueError(f"head_size must be positive, got {self.head_size}")
         if not (0 <= self.rotate_dim <= self.head_size and self.rotate_dim % 2 == 0):
             raise ValueError(f"rotate_dim must be even and at most head_size ({self.head_size}), got {self.rotate_dim}")
         if self.conv_taps < 1 or self.window < 1 or self.keep_first < 0:

@@ -288,6 +288,8 @@ ATTN = {
     "plain": O.parallel_layer(heads=1, kv_heads=1, dim=8, conv=1, window=500, keep_first=0, rot_dims=8, scale=0.35)["mixer"]["left"],
     # no rotation at all, more kept tokens than the window is long, two taps
     "sinks": O.parallel_layer(heads=4, kv_heads=4, dim=16, conv=2, window=5, keep_first=9, rot_dims=0, scale=0.25)["mixer"]["left"],
+    # an odd head size: the last entry of every head has no partner and is never rotated
+    "odd_head": O.parallel_layer(heads=3, kv_heads=1, dim=7, conv=3, window=9, keep_first=1, rot_dims=6, scale=0.4)["mixer"]["left"],
     # head sizes the tensor-core kernels take in bf16: grouped heads, a window that ends inside a 128-key page, kept keys
     "tc64": O.parallel_layer(heads=4, kv_heads=2, dim=64, conv=3, window=21, keep_first=2, rot_dims=32, scale=0.125)["mixer"]["left"],
     "tc128": O.parallel_layer(heads=8, kv_heads=1, dim=128, conv=4, window=50, keep_first=5, rot_dims=64, base=1e5, scale=0.09)["mixer"]["left"],
