@@ -23,6 +23,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../common/host.h"
 
@@ -263,10 +264,19 @@ window_attention_kernel(const T* __restrict__ q, long long q_ld, const T* __rest
 // A block owns SCAN_THREADS / R columns of the d x dv state of one (sequence, head) and walks the sequence's new tokens in order (the
 // columns of these recurrences do not interact).  Thread (col, r) -- r varying fastest, R a power of two <= 32 -- holds rows r RPT ..
 // r RPT + RPT - 1 of its column in registers (its q / k values are consecutive in shared memory: 16-byte loads); sums over rows are finished by a butterfly over the R lanes.  The state is kept in global memory in thread
-// order ([column tile][RPT][SCAN_THREADS], opaque to everything but these kernels, coalesced).  Inputs travel in chunks of `ch` tokens
+// order ([column tile][column of the thread][RPT][SCAN_THREADS], opaque to everything but these kernels, coalesced).  Inputs travel in chunks of `ch` tokens
 // (a power of two <= 16 with at most SCAN_PF * SCAN_THREADS staged values per array): while a chunk is consumed from shared memory the
 // next one is already on its way in registers, so the walk never waits for global memory.
-constexpr int SCAN_THREADS = 256, SCAN_PF = 8;
+constexpr int SCAN_THREADS = 256, SCAN_PF = 8, SCAN_CPT = 2;  // SCAN_CPT: columns of the state per thread (staged q / k rows serve both)
+
+// Where row i of a staged q / k / decay vector sits in its shared-memory row: thread r reads its rows r RPT .. r RPT + RPT - 1 four at a
+// time, and the four-row groups of the R lanes lie side by side ([group][lane][4]) so that one 16-byte load of the R lanes covers a
+// contiguous 16 R bytes (no bank conflicts; rows laid out plainly put lanes 32 bytes apart, a 4-way conflict).
+template <int RPT, int R>
+__device__ __forceinline__ int staged_pos(int i) {
+  const int r = i / RPT, ii = i % RPT;
+  return (ii >> 2) * (R * 4) + r * 4 + (ii & 3);
+}
 
 template <int R>
 __device__ __forceinline__ float lanes_sum(float v) {
@@ -286,29 +296,30 @@ matrix_memory_scan_kernel(const T* __restrict__ proj, long long ld, int q_col0, 
                           float* __restrict__ state_S, float* __restrict__ state_n, float* __restrict__ state_m, float* __restrict__ out, int H, int d,
                           int dv, int ch) {
   extern __shared__ __align__(16) float sm[];
-  constexpr int nthr = SCAN_THREADS, CB = nthr / R, DP = R * RPT;  // DP: a staged q / k row, padded with zeros past d
+  constexpr int nthr = SCAN_THREADS, CB = nthr / R, CBT = SCAN_CPT * CB, DP = R * RPT;  // DP: a staged q / k row, padded with zeros past d
   const int4 sd = seq_desc[blockIdx.x];
   const int h = blockIdx.y, tid = threadIdx.x;
   const bool gate_warp = tid >= nthr;
-  const int col0 = blockIdx.z * CB, lc = (tid % nthr) / R, r = tid % R, col = col0 + lc;
-  const bool live = !gate_warp && col < dv;
-  const int ncol = min(CB, dv - col0);
-  // per buffer: q [ch DP] | k [ch DP] | v [ch CB] | a [ch] | b [ch] | e [ch] | pad [ch]; then the gate warp's scratch (2 ch)
-  const int buf = 2 * ch * DP + ch * CB + 4 * ch;  // (a multiple of 4 floats: rows are read 16 bytes at a time)
+  const int col0 = blockIdx.z * CBT, lc = (tid % nthr) / R, r = tid % R, col = col0 + lc;  // the thread's columns: col and col + CB
+  const bool live = !gate_warp && col < dv, live2 = !gate_warp && col + CB < dv;
+  const int ncol = min(CBT, dv - col0);
+  // per buffer: q [ch DP] | k [ch DP] | v [ch CBT] | a [ch] | b [ch] | e [ch] | pad [ch]; then the gate warp's scratch (2 ch)
+  const int buf = 2 * ch * DP + ch * CBT + 4 * ch;  // (a multiple of 4 floats: rows are read 16 bytes at a time)
   float* tmp_g = sm + 2 * buf;
   if (d != DP)
     for (int x = tid; x < 2 * buf; x += nthr + 32) sm[x] = 0.f;  // the padding of the rows stays zero from here on
-  float S[RPT], nn[RPT];
-  float* gS = state_S + ((static_cast<size_t>(sd.w) * H + h) * gridDim.z + blockIdx.z) * RPT * nthr;
+  float S[RPT], S2[RPT], nn[RPT];
+  float* gS = state_S + ((static_cast<size_t>(sd.w) * H + h) * gridDim.z + blockIdx.z) * SCAN_CPT * RPT * nthr;
   float* gn = state_n + (static_cast<size_t>(sd.w) * H + h) * d;
   float m = 0.f;  // followed by the gate warp only
 #pragma unroll
-  for (int ii = 0; ii < RPT; ++ii) S[ii] = nn[ii] = 0.f;
+  for (int ii = 0; ii < RPT; ++ii) S[ii] = S2[ii] = nn[ii] = 0.f;
   if (sd.z > 0) {
     if (!gate_warp) {
 #pragma unroll
       for (int ii = 0; ii < RPT; ++ii) {
         S[ii] = gS[ii * nthr + tid];
+        S2[ii] = gS[(RPT + ii) * nthr + tid];
         const int i = r * RPT + ii;
         nn[ii] = i < d ? gn[i] : 0.f;
       }
@@ -355,15 +366,15 @@ matrix_memory_scan_kernel(const T* __restrict__ proj, long long ld, int q_col0, 
         int tok, c;
         split_qk(tid + e * nthr, tok, c);
         if (tok < cn) {
-          bq[tok * DP + c] = to_f(pq[e]) * qscale;
-          bk[tok * DP + c] = to_f(pk[e]);
+          bq[tok * DP + staged_pos<RPT, R>(c)] = to_f(pq[e]) * qscale;
+          bk[tok * DP + staged_pos<RPT, R>(c)] = to_f(pk[e]);
         }
         split_v(tid + e * nthr, tok, c);
-        if (tok < cn) bv[tok * CB + c] = to_f(pv[e]);
+        if (tok < cn) bv[tok * CBT + c] = to_f(pv[e]);
       }
       return;
     }
-    float* ga = bv + ch * CB;
+    float* ga = bv + ch * CBT;
     float* gb = ga + ch;
     float* ge = gb + ch;
     const int lane = tid - nthr;
@@ -396,34 +407,39 @@ matrix_memory_scan_kernel(const T* __restrict__ proj, long long ld, int q_col0, 
     const bool more = t0 + ch < sd.y;
     if (more) fetch(t0 + ch);
     if (!gate_warp) {
-      const float* bq = sm + cur * buf + r * RPT;
+      const float* bq = sm + cur * buf + r * 4;
       const float* bk = bq + ch * DP;
       const float* bv = sm + cur * buf + 2 * ch * DP;
-      const float* ga = bv + ch * CB;
+      const float* ga = bv + ch * CBT;
       const float* gb = ga + ch;
       const float* ge = gb + ch;
       float* orow = out + static_cast<size_t>(sd.x + t0) * H * dv + h * dv + col;
 #pragma unroll 2
       for (int x = 0; x < cn; ++x) {
         const float a = ga[x], b2 = gb[x];
-        const float v = live ? bv[x * CB + lc] : 0.f;
-        float po = 0.f, pn = 0.f;
+        const float v = live ? bv[x * CBT + lc] : 0.f, v2 = live2 ? bv[x * CBT + CB + lc] : 0.f;
+        float po = 0.f, po2 = 0.f, pn = 0.f;
 #pragma unroll
         for (int i4 = 0; i4 < RPT; i4 += 4) {
-          const float4 k4 = *reinterpret_cast<const float4*>(bk + x * DP + i4), q4 = *reinterpret_cast<const float4*>(bq + x * DP + i4);
+          const float4 k4 = *reinterpret_cast<const float4*>(bk + x * DP + i4 * R), q4 = *reinterpret_cast<const float4*>(bq + x * DP + i4 * R);
           const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float bk2 = b2 * kk[j];
             S[i4 + j] = fmaf(a, S[i4 + j], bk2 * v);
+            S2[i4 + j] = fmaf(a, S2[i4 + j], bk2 * v2);
             nn[i4 + j] = fmaf(a, nn[i4 + j], bk2);
             po = fmaf(S[i4 + j], qq[j], po);
+            po2 = fmaf(S2[i4 + j], qq[j], po2);
             pn = fmaf(nn[i4 + j], qq[j], pn);
           }
         }
         po = lanes_sum<R>(po);
+        po2 = lanes_sum<R>(po2);
         pn = lanes_sum<R>(pn);
-        if (live && r == 0) orow[static_cast<size_t>(x) * H * dv] = po / (fmaxf(fabsf(pn), ge[x]) + 1e-6f);
+        const float den = fmaxf(fabsf(pn), ge[x]) + 1e-6f;
+        if (live && r == 0) orow[static_cast<size_t>(x) * H * dv] = po / den;
+        if (live2 && r == 0) orow[static_cast<size_t>(x) * H * dv + CB] = po2 / den;
       }
     }
     if (more) stage(t0 + ch, sm + (cur ^ 1) * buf);
@@ -433,6 +449,7 @@ matrix_memory_scan_kernel(const T* __restrict__ proj, long long ld, int q_col0, 
 #pragma unroll
     for (int ii = 0; ii < RPT; ++ii) {
       gS[ii * nthr + tid] = S[ii];
+      gS[(RPT + ii) * nthr + tid] = S2[ii];
       const int i = r * RPT + ii;
       if (col == 0 && i < d) gn[i] = nn[ii];  // every column tile carries the same n; the first one keeps it
     }
@@ -449,19 +466,22 @@ delta_rule_scan_kernel(const float* __restrict__ qn, const float* __restrict__ k
                        const float* __restrict__ decay, const int4* __restrict__ seq_desc, float* __restrict__ state_S, float* __restrict__ out,
                        int H, int G, int d, int dv, int ch) {
   extern __shared__ __align__(16) float sm[];
-  constexpr int nthr = SCAN_THREADS, CB = nthr / R, DP = R * RPT;
+  constexpr int nthr = SCAN_THREADS, CB = nthr / R, CBT = SCAN_CPT * CB, DP = R * RPT;
   const int4 sd = seq_desc[blockIdx.x];
   const int h = blockIdx.y, g = h / (H / G), tid = threadIdx.x;
-  const int col0 = blockIdx.z * CB, lc = tid / R, r = tid % R, col = col0 + lc;
-  const bool live = col < dv;
-  const int ncol = min(CB, dv - col0);
-  const int buf = 3 * ch * DP + ch * CB + ((ch + 3) & ~3);  // q | k | decay | v | beta (a multiple of 4 floats)
+  const int col0 = blockIdx.z * CBT, lc = tid / R, r = tid % R, col = col0 + lc;  // the thread's columns: col and col + CB
+  const bool live = col < dv, live2 = col + CB < dv;
+  const int ncol = min(CBT, dv - col0);
+  const int buf = 3 * ch * DP + ch * CBT + ((ch + 3) & ~3);  // q | k | decay | v | beta (a multiple of 4 floats)
   if (d != DP)
     for (int x = tid; x < 2 * buf; x += nthr) sm[x] = 0.f;  // the padding of the rows stays zero from here on
-  float S[RPT];
-  float* gS = state_S + ((static_cast<size_t>(sd.w) * H + h) * gridDim.z + blockIdx.z) * RPT * nthr;
+  float S[RPT], S2[RPT];
+  float* gS = state_S + ((static_cast<size_t>(sd.w) * H + h) * gridDim.z + blockIdx.z) * SCAN_CPT * RPT * nthr;
 #pragma unroll
-  for (int ii = 0; ii < RPT; ++ii) S[ii] = sd.z > 0 ? gS[ii * nthr + tid] : 0.f;
+  for (int ii = 0; ii < RPT; ++ii) {
+    S[ii] = sd.z > 0 ? gS[ii * nthr + tid] : 0.f;
+    S2[ii] = sd.z > 0 ? gS[(RPT + ii) * nthr + tid] : 0.f;
+  }
   const int lg_d = (d & (d - 1)) == 0 ? __ffs(d) - 1 : -1, lg_c = (ncol & (ncol - 1)) == 0 ? __ffs(ncol) - 1 : -1;
   auto split_qk = [&](int x, int& tok, int& c) {
     if (lg_d >= 0) { tok = x >> lg_d; c = x & (d - 1); } else { tok = x / d; c = x - tok * d; }
@@ -494,18 +514,19 @@ delta_rule_scan_kernel(const float* __restrict__ qn, const float* __restrict__ k
     float* bk = bq + ch * DP;
     float* bg = bk + ch * DP;
     float* bv = bg + ch * DP;
-    float* bb = bv + ch * CB;
+    float* bb = bv + ch * CBT;
 #pragma unroll
     for (int e = 0; e < SCAN_PF; ++e) {
       int tok, c;
       split_qk(tid + e * nthr, tok, c);
       if (tok < cn) {
-        bq[tok * DP + c] = pq[e];
-        bk[tok * DP + c] = pk[e];
-        bg[tok * DP + c] = pg[e];
+        const int pos = tok * DP + staged_pos<RPT, R>(c);
+        bq[pos] = pq[e];
+        bk[pos] = pk[e];
+        bg[pos] = pg[e];
       }
       split_v(tid + e * nthr, tok, c);
-      if (tok < cn) bv[tok * CB + c] = pv[e];
+      if (tok < cn) bv[tok * CBT + c] = pv[e];
     }
     if (tid < cn) bb[tid] = pb;
   };
@@ -518,42 +539,58 @@ delta_rule_scan_kernel(const float* __restrict__ qn, const float* __restrict__ k
     const int cn = min(ch, sd.y - t0);
     const bool more = t0 + ch < sd.y;
     if (more) fetch(t0 + ch);
-    const float* bq = sm + cur * buf + r * RPT;
+    const float* bq = sm + cur * buf + r * 4;
     const float* bk = bq + ch * DP;
     const float* bg = bk + ch * DP;
     const float* bv = sm + cur * buf + 3 * ch * DP;
-    const float* bb = bv + ch * CB;
+    const float* bb = bv + ch * CBT;
     float* orow = out + static_cast<size_t>(sd.x + t0) * H * dv + h * dv + col;
     for (int x = 0; x < cn; ++x) {
-      float ps0 = 0.f, ps1 = 0.f;
+      float ps = 0.f, ps2 = 0.f;
       float kk[RPT];
 #pragma unroll
       for (int i4 = 0; i4 < RPT; i4 += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(bk + x * DP + i4), g4 = *reinterpret_cast<const float4*>(bg + x * DP + i4);
+        const float4 k4 = *reinterpret_cast<const float4*>(bk + x * DP + i4 * R), g4 = *reinterpret_cast<const float4*>(bg + x * DP + i4 * R);
+        const float gg[4] = {g4.x, g4.y, g4.z, g4.w};  // padded rows: decay 0 on a state of 0
         kk[i4] = k4.x; kk[i4 + 1] = k4.y; kk[i4 + 2] = k4.z; kk[i4 + 3] = k4.w;
-        S[i4] *= g4.x; S[i4 + 1] *= g4.y; S[i4 + 2] *= g4.z; S[i4 + 3] *= g4.w;  // padded rows: decay 0 on a state of 0
-        ps0 = fmaf(S[i4], k4.x, ps0); ps1 = fmaf(S[i4 + 1], k4.y, ps1);
-        ps0 = fmaf(S[i4 + 2], k4.z, ps0); ps1 = fmaf(S[i4 + 3], k4.w, ps1);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          S[i4 + j] *= gg[j];
+          S2[i4 + j] *= gg[j];
+          ps = fmaf(S[i4 + j], kk[i4 + j], ps);
+          ps2 = fmaf(S2[i4 + j], kk[i4 + j], ps2);
+        }
       }
-      const float ps = lanes_sum<R>(ps0 + ps1);
-      const float u = live ? bb[x] * (bv[x * CB + lc] - ps) : 0.f;
-      float po0 = 0.f, po1 = 0.f;
+      ps = lanes_sum<R>(ps);
+      ps2 = lanes_sum<R>(ps2);
+      const float bx = bb[x];
+      const float u = live ? bx * (bv[x * CBT + lc] - ps) : 0.f, u2 = live2 ? bx * (bv[x * CBT + CB + lc] - ps2) : 0.f;
+      float po = 0.f, po2 = 0.f;
 #pragma unroll
       for (int i4 = 0; i4 < RPT; i4 += 4) {
-        const float4 q4 = *reinterpret_cast<const float4*>(bq + x * DP + i4);
-        S[i4] = fmaf(kk[i4], u, S[i4]); S[i4 + 1] = fmaf(kk[i4 + 1], u, S[i4 + 1]);
-        S[i4 + 2] = fmaf(kk[i4 + 2], u, S[i4 + 2]); S[i4 + 3] = fmaf(kk[i4 + 3], u, S[i4 + 3]);
-        po0 = fmaf(S[i4], q4.x, po0); po1 = fmaf(S[i4 + 1], q4.y, po1);
-        po0 = fmaf(S[i4 + 2], q4.z, po0); po1 = fmaf(S[i4 + 3], q4.w, po1);
+        const float4 q4 = *reinterpret_cast<const float4*>(bq + x * DP + i4 * R);
+        const float qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          S[i4 + j] = fmaf(kk[i4 + j], u, S[i4 + j]);
+          S2[i4 + j] = fmaf(kk[i4 + j], u2, S2[i4 + j]);
+          po = fmaf(S[i4 + j], qq[j], po);
+          po2 = fmaf(S2[i4 + j], qq[j], po2);
+        }
       }
-      const float po = lanes_sum<R>(po0 + po1);
+      po = lanes_sum<R>(po);
+      po2 = lanes_sum<R>(po2);
       if (live && r == 0) orow[static_cast<size_t>(x) * H * dv] = po;
+      if (live2 && r == 0) orow[static_cast<size_t>(x) * H * dv + CB] = po2;
     }
     if (more) stage(t0 + ch, sm + (cur ^ 1) * buf);
     __syncthreads();
   }
 #pragma unroll
-  for (int ii = 0; ii < RPT; ++ii) gS[ii * nthr + tid] = S[ii];
+  for (int ii = 0; ii < RPT; ++ii) {
+    gS[ii * nthr + tid] = S[ii];
+    gS[(RPT + ii) * nthr + tid] = S2[ii];
+  }
 }
 
 // One block per token.  proj row holds the q [G d], k [G d] and v [H dv] projections at q_col0 / k_col0 / v_col0; the kept rows of the
@@ -632,12 +669,13 @@ using namespace dsb::recur;
 // chunk: about 8 rows per thread (a short dependent chain per token); a block of SCAN_THREADS threads then covers SCAN_THREADS / R columns.
 static bool scan_shape(int d, int dv, int* R, int* RPT, int* tiles, int* chunk = nullptr) {
   if (d < 1 || dv < 1 || d > SCAN_PF * SCAN_THREADS) return false;
+  static const int rows_target = [] { const char* e = getenv("DSB200_SCAN_ROWS"); const int v = e ? atoi(e) : 0; return v >= 4 && v <= 64 ? v : 8; }();
   int r = 1;
-  while (r < 32 && (d + r - 1) / r > 8) r <<= 1;
+  while (r < 32 && (d + r - 1) / r > rows_target) r <<= 1;
   const int need = (d + r - 1) / r;
   int rpt = 8;
   while (rpt < need) rpt <<= 1;
-  const int cols = SCAN_THREADS / r;
+  const int cols = SCAN_CPT * (SCAN_THREADS / r);  // columns per block
   *R = r;
   *RPT = rpt;
   *tiles = (dv + cols - 1) / cols;
@@ -653,7 +691,7 @@ static bool scan_shape(int d, int dv, int* R, int* RPT, int* tiles, int* chunk =
 DSB_EXPORT long long dsb200_scan_state_floats(int d, int dv) {
   int R, RPT, tiles;
   if (!scan_shape(d, dv, &R, &RPT, &tiles)) return -1;
-  return static_cast<long long>(tiles) * RPT * SCAN_THREADS;
+  return static_cast<long long>(tiles) * SCAN_CPT * RPT * SCAN_THREADS;
 }
 
 #define SCAN_DISPATCH(RPTv, Rv, CALL) \
@@ -748,7 +786,7 @@ DSB_EXPORT int dsb200_matrix_memory_scan(const void* proj, long long ld, int q_c
   int R, RPT, tiles, ch;
   DSB_REQUIRE(scan_shape(d, dv, &R, &RPT, &tiles, &ch), "matrix_memory_scan: a %d x %d state per head is not supported", d, dv);
   const int threads = SCAN_THREADS + 32;
-  const size_t smem = (2 * static_cast<size_t>(2 * ch * R * RPT + ch * (SCAN_THREADS / R) + 4 * ch) + 2 * ch) * sizeof(float);
+  const size_t smem = (2 * static_cast<size_t>(2 * ch * R * RPT + ch * SCAN_CPT * (SCAN_THREADS / R) + 4 * ch) + 2 * ch) * sizeof(float);
   DSB_REQUIRE(smem <= 200 * 1024, "matrix_memory_scan: head sizes %d / %d do not fit shared memory", d, dv);
   const dim3 grid(n_seqs, H, tiles);
   bool launched = false;
@@ -816,7 +854,7 @@ DSB_EXPORT int dsb200_delta_rule_scan(const float* qn, const float* kn, const fl
   DSB_REQUIRE(H % G == 0 && scan_shape(d, dv, &R, &RPT, &tiles, &ch), "delta_rule_scan: heads %d / %d, a %d x %d state per head is not supported", H, G, d,
               dv);
   const int threads = SCAN_THREADS;
-  const size_t smem = 2 * static_cast<size_t>(3 * ch * R * RPT + ch * (SCAN_THREADS / R) + ((ch + 3) & ~3)) * sizeof(float);
+  const size_t smem = 2 * static_cast<size_t>(3 * ch * R * RPT + ch * SCAN_CPT * (SCAN_THREADS / R) + ((ch + 3) & ~3)) * sizeof(float);
   DSB_REQUIRE(smem <= 200 * 1024, "delta_rule_scan: head sizes %d / %d do not fit shared memory", d, dv);
   const dim3 grid(n_seqs, H, tiles);
   bool launched = false;
