@@ -107,6 +107,23 @@ __device__ __forceinline__ float conv_at(const T* __restrict__ u, long long ld, 
   return acc;
 }
 
+// The same for a token whose taps all lie among the new rows (i >= taps - 1: every token of a portion but its first taps - 1): no
+// selection per tap, the four weights of a 4-tap filter in one load.  Same order of additions as conv_at.
+template <typename T>
+__device__ __forceinline__ float conv_inside(const T* __restrict__ u, long long ld, const float* __restrict__ w, int taps, int i) {
+  const T* p = u + static_cast<long long>(i - (taps - 1)) * ld;
+  if (taps == 4) {
+    const float4 w4 = *reinterpret_cast<const float4*>(w);
+    float acc = w4.x * to_f(p[0]);
+    acc = fmaf(w4.y, to_f(p[ld]), acc);
+    acc = fmaf(w4.z, to_f(p[2 * ld]), acc);
+    return fmaf(w4.w, to_f(p[3 * ld]), acc);
+  }
+  float acc = 0.f;
+  for (int j = 0; j < taps; ++j, p += ld) acc = fmaf(w[j], to_f(*p), acc);
+  return acc;
+}
+
 // state [slots, taps - 1, st_ld], columns st_col0 .. st_col0 + C: after the step, row j holds the projected values of position
 // seen + n - (taps - 1) + j.
 template <typename T>
@@ -149,11 +166,13 @@ __global__ void window_qk_prepare_kernel(const T* __restrict__ proj, long long l
   T* krow = cache + ((static_cast<size_t>(blk) * 2 + 0) * block_size + pos % block_size) * nk;
   T* vrow = cache + ((static_cast<size_t>(blk) * 2 + 1) * block_size + pos % block_size) * nk;
   float sq = 0.f, sk = 0.f;
+  const bool inside = i >= taps - 1;  // (the same for the whole block)
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     const bool is_q = c < nq;
     const int cc = is_q ? c : c - nq;
-    const float v = conv_at(u0 + (is_q ? q_col0 : k_col0) + cc, ld, st + c, C, (is_q ? conv_q : conv_k) + static_cast<size_t>(cc) * taps, taps, i,
-                            sd.z);
+    const T* uc = u0 + (is_q ? q_col0 : k_col0) + cc;
+    const float* wc = (is_q ? conv_q : conv_k) + static_cast<size_t>(cc) * taps;
+    const float v = inside ? conv_inside(uc, ld, wc, taps, i) : conv_at(uc, ld, st + c, C, wc, taps, i, sd.z);
     y[c] = v;
     if (is_q) sq += v * v;
     else {
@@ -176,8 +195,9 @@ __global__ void window_qk_prepare_kernel(const T* __restrict__ proj, long long l
   const float inv_q = 1.f / sqrtf(sq / static_cast<float>(nq) + eps), inv_k = 1.f / sqrtf(sk / static_cast<float>(nk) + eps);
   T* qrow = q_out + static_cast<long long>(t) * q_ld;
   const int hp = (d + 1) / 2;  // pairs (2p, 2p + 1) per head; the last one of an odd head size has no second entry
+  const int lg_hp = (hp & (hp - 1)) == 0 ? __ffs(hp) - 1 : -1;
   for (int pr = threadIdx.x; pr < (H + G) * hp; pr += blockDim.x) {
-    const int head = pr / hp, within = 2 * (pr - head * hp);
+    const int head = lg_hp >= 0 ? pr >> lg_hp : pr / hp, within = 2 * (pr - head * hp);
     const int c = head * d + within;
     const bool is_q = c < nq, two = within + 1 < d;
     const int cc = is_q ? c : c - nq;
@@ -614,6 +634,7 @@ __global__ void delta_prepare_kernel(const T* __restrict__ proj, long long ld, i
   const T* u0 = proj + static_cast<long long>(sd.x) * ld;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const float qscale = 1.f / sqrtf(static_cast<float>(d));
+  const bool inside = i >= taps - 1;  // (the same for the whole block)
   for (int hh = warp; hh < 2 * G; hh += nw) {  // head hh of (q heads | k heads)
     const int which = hh < G ? 0 : 1;
     const int c0 = hh * d;  // first channel of the head among the 2 G d
@@ -621,7 +642,9 @@ __global__ void delta_prepare_kernel(const T* __restrict__ proj, long long ld, i
     const float* w = (which ? conv_k : conv_q) + static_cast<size_t>(hh - which * G) * d * taps;
     float ss = 0.f;
     for (int c = lane; c < d; c += 32) {
-      const float val = siluf_(conv_at(u0 + col0 + c, ld, st + c0 + c, C, w + static_cast<size_t>(c) * taps, taps, i, sd.z));
+      const float cv = inside ? conv_inside(u0 + col0 + c, ld, w + static_cast<size_t>(c) * taps, taps, i)
+                              : conv_at(u0 + col0 + c, ld, st + c0 + c, C, w + static_cast<size_t>(c) * taps, taps, i, sd.z);
+      const float val = siluf_(cv);
       y[c0 + c] = val;
       ss += val * val;
     }
@@ -630,11 +653,15 @@ __global__ void delta_prepare_kernel(const T* __restrict__ proj, long long ld, i
     float* dst = (which ? kn : qn) + static_cast<size_t>(t) * nqk + (hh - which * G) * d;
     for (int c = lane; c < d; c += 32) dst[c] = y[c0 + c] * inv;  // each lane re-reads what it wrote
   }
-  for (int c = threadIdx.x; c < nv; c += blockDim.x)
-    vo[static_cast<size_t>(t) * nv + c] = siluf_(conv_at(u0 + v_col0 + c, ld, st + 2 * nqk + c, C, conv_v + static_cast<size_t>(c) * taps, taps, i, sd.z));
-  for (int c = threadIdx.x; c < H * d; c += blockDim.x) {
-    float* a = a_pre + static_cast<size_t>(t) * H * d + c;
-    *a = expf(-expf(A_log[c / d]) * softplusf_(*a + dt_bias[c]));
+  for (int c = threadIdx.x; c < nv; c += blockDim.x) {
+    const float cv = inside ? conv_inside(u0 + v_col0 + c, ld, conv_v + static_cast<size_t>(c) * taps, taps, i)
+                            : conv_at(u0 + v_col0 + c, ld, st + 2 * nqk + c, C, conv_v + static_cast<size_t>(c) * taps, taps, i, sd.z);
+    vo[static_cast<size_t>(t) * nv + c] = siluf_(cv);
+  }
+  for (int hh = warp; hh < H; hh += nw) {  // a warp per head: the head's rate once, no division per channel
+    const float rate = expf(A_log[hh]);
+    float* a = a_pre + static_cast<size_t>(t) * H * d + hh * d;
+    for (int c = lane; c < d; c += 32) a[c] = expf(-rate * softplusf_(a[c] + dt_bias[hh * d + c]));
   }
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     float* bp = beta_pre + static_cast<size_t>(t) * H + c;
@@ -720,7 +747,10 @@ DSB_EXPORT int dsb200_window_qk_prepare(const void* proj, long long ld, int q_co
               "window_qk_prepare: heads %d / %d, head size %d, rotated %d, taps %d", H, G, d, rot_dims, taps);
   const size_t smem = (static_cast<size_t>(H + G) * d + rot_dims) * sizeof(float);
   DSB_REQUIRE(smem <= 200 * 1024, "window_qk_prepare: (H + G) d = %d does not fit shared memory", (H + G) * d);
-  const int block = (H + G) * d >= 2048 ? 512 : 256;
+  static const int block_env = [] { const char* e = getenv("DSB200_PREP_BLOCK"); return e ? atoi(e) : 0; }();
+  // many tokens: small blocks (more tokens in flight per SM); few tokens (decode steps): many threads per token (a short chain per thread)
+  const int few = min(1024, max(128, (((H + G) * d + 3) / 4 + 31) / 32 * 32));
+  const int block = block_env >= 64 && block_env <= 1024 ? block_env : (n_tokens >= 512 ? 256 : few);
 #define LAUNCH(T)                                                                                                                          \
   do {                                                                                                                                     \
     if (smem > 48 * 1024) DSB_CHECK_CUDA(cudaFuncSetAttribute(window_qk_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
@@ -828,7 +858,9 @@ DSB_EXPORT int dsb200_delta_prepare(const void* proj, long long ld, int q_col0, 
   if (n_tokens == 0) return DSB_OK;
   const size_t smem = 2 * static_cast<size_t>(G) * d * sizeof(float);
   DSB_REQUIRE(smem <= 200 * 1024, "delta_prepare: 2 G d = %d does not fit shared memory", 2 * G * d);
-  const int block = 2 * G * d + H * dv >= 2048 ? 512 : 256;
+  static const int block_env = [] { const char* e = getenv("DSB200_PREP_BLOCK"); return e ? atoi(e) : 0; }();
+  const int few = min(1024, max(128, ((2 * G * d + H * dv + 3) / 4 + 31) / 32 * 32));
+  const int block = block_env >= 64 && block_env <= 1024 ? block_env : (n_tokens >= 512 ? 256 : few);
 #define LAUNCH(T)                                                                                                                       \
   do {                                                                                                                                  \
     if (smem > 48 * 1024) DSB_CHECK_CUDA(cudaFuncSetAttribute(delta_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
